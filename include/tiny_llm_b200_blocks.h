@@ -41,18 +41,23 @@ int tlb_embed_rows(const int32_t *ids, const void *table, float *x32, void *h, i
 int tlb_norm_residual(const void *y, int y_is_f32, const void *w, float weight_offset, const void *scale, float eps, float *residual,
                       void *h, int rows, int dim, int dtype, void *stream);
 
-/* End of a layer whose sublayers read one norm of the stream, fused with the next norm: residual += a (+ b, if b != NULL)
- * in fp32, then, if w != NULL, h = residual / rms(residual) * w rounded to `dtype`. */
-int tlb_add_norm(float *residual, const float *a, const float *b, const void *w, float eps, void *h, int rows, int dim, int dtype, void *stream);
+/* End of a sublayer, fused with the next norm: residual += a (+ b, if b != NULL) in fp32, then, if w != NULL,
+ * h = residual / rms(residual) * w rounded to `dtype`.  a_row != 0: `a` is one row [dim] added to every row. */
+int tlb_add_norm(float *residual, const float *a, int a_row, const float *b, const void *w, float eps, void *h, int rows, int dim, int dtype,
+                 void *stream);
 
 /* y = coef * (a / rms(a) * wa + b / rms(b) * wb); a, b, y fp32 [rows, dim], wa, wb `dtype` [dim]. */
 int tlb_norm_mix2(const float *a, const void *wa, const float *b, const void *wb, float coef, float eps, float *y, int rows, int dim, int dtype,
                   void *stream);
 
 /* Rotary positions, in place, on `dims` entries starting at `first` within every head of x [rows, heads] (strides in
- * elements).  interleaved = 0: pair (i, i + dims/2); 1: pair (2i, 2i+1).  angle = tok_pos[row] * base^(-2i/dims). */
+ * elements).  interleaved = 0: pair (i, i + dims/2); 1: pair (2i, 2i+1).  angle = tok_pos[row] * base^(-2i/dims) / factor
+ * (factor 1 = none: linear scaling of the positions). */
 int tlb_rope_rows(void *x, long long row_stride, long long head_stride, int first, int heads, int dims, int interleaved, double base,
-                  const int32_t *tok_pos, int rows, int dtype, void *stream);
+                  double factor, const int32_t *tok_pos, int rows, int dtype, void *stream);
+/* The same angles as fp32 tables cos_out, sin_out [rows, dims / 2], for kernels that rotate in fp32 on their way into a
+ * recurrence (tlb_decay_scan). */
+int tlb_rope_table(const int32_t *tok_pos, int rows, int dims, double base, double factor, float *cos_out, float *sin_out, void *stream);
 
 /* Latent cache append: for every token, the first `rank` entries of down[t,:] are RMS-normed (plain weight) and the last
  * `rot` entries rotated by the token's position; both are stored at the token's slot of slab [pages, page_size, rank+rot]
@@ -126,8 +131,11 @@ int tlb_kv_prepare(void *q, long long q_token, long long q_head, int heads, cons
                    const int32_t *tok_pos, const int32_t *tok_seq, const int32_t *block_table, int max_pages, int num_pages, int page_size,
                    void *slab, int tokens, int dtype, void *stream);
 
-/* Linear attention with a per-channel decay, state in fp32 slots.  Per sequence and head S [dk, dv]:
- *   alpha = sigmoid(z + z_bias)^(1 / tau);  S <- diag(alpha) S + k v^T;  out = S^T (q_scale * q)
+/* Linear attention with a decay, state in fp32 slots.  Per sequence and head S [dk, dv]:
+ *   alpha = sigmoid(z + z_bias)^(1 / tau) per key channel, or (head_decay != NULL; z may be NULL) the fixed head_decay[head];
+ *   S <- diag(alpha) S + k v^T;  out = S^T (q_scale * q)
+ * rope_dims > 0: the first rope_dims entries of every head of q and k are rotated first, in fp32, by the angles tabulated
+ * per flat token in rope_cos, rope_sin [T, rope_dims / 2] (pairs (2i, 2i+1) if rope_interleaved, else (i, i + rope_dims/2)).
  * seq_info [num_seqs, 4] int32: first flat token, token count, position of the first token, state slot.  A sequence at
  * position 0 starts from zero; the slot (state + slot * slot_stride floats, [heads, dk, dv]) is written after the last
  * token.  q, k [T, heads, dk], v [T, heads, dv] views (strides in elements), z [T, heads * dk] fp32 rows z_token apart,
@@ -139,22 +147,49 @@ int tlb_kv_prepare(void *q, long long q_token, long long q_head, int heads, cons
 #define TLB_DECAY_SCAN_SEGMENT 64
 size_t tlb_decay_scan_workspace(int num_seqs, int max_tokens_per_seq, int heads, int dk, int dv);
 int tlb_decay_scan(const void *q, long long q_token, long long q_head, const void *k, long long k_token, long long k_head, const void *v,
-                   long long v_token, long long v_head, const float *z, long long z_token, const void *z_bias, float tau, float q_scale, int heads,
+                   long long v_token, long long v_head, const float *z, long long z_token, const void *z_bias, float tau, const float *head_decay,
+                   const float *rope_cos, const float *rope_sin, int rope_dims, int rope_interleaved, float q_scale, int heads,
                    int dk, int dv, const int32_t *seq_info, int num_seqs, int max_tokens_per_seq, float *state, long long slot_stride,
                    int num_slots, float *out, void *workspace, size_t workspace_bytes, int dtype, void *stream);
-/* out[t, h, :] = o[t, h, :] / rms(o[t, h, :]) * w * act(gate[t, h, :]) (gate rows g_token apart, NULL = no gate; act 0 = the gate
- * as it is, 1 = silu); o fp32 [tokens, heads, dv], out `dtype` [tokens, heads * dv]. */
+/* out[t, h, :] = o[t, h, :] / rms(o[t, h, :]) * w * act(gate[t, h, :]) (w NULL = no weight; gate rows g_token apart, NULL = no
+ * gate; act 0 = the gate as it is, 1 = silu, 2 = sigmoid); o fp32 [tokens, heads, dv], out `dtype` [tokens, heads * dv]. */
 int tlb_head_norm_gate(const float *o, const void *w, float eps, const void *gate, long long g_token, int act, void *out, int tokens, int heads,
                        int dv, int dtype, void *stream);
+
+/* Gated delta rule, state in fp32 slots.  Per sequence and head S [dk, dv], token by token:
+ *   S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T;  out = S^T q
+ *   g = exp(-exp(a_log[head]) * softplus(a + dt_bias)), beta = sigmoid(b); q, k made unit vectors per head
+ *   (x / sqrt(sum x^2 + unit_eps)), q times q_scale.  per_channel: a [T, heads * dk] and dt_bias [heads * dk] give one decay
+ *   per key channel; else a [T, heads], dt_bias [heads] one per head.  a is fp32 (a_is_f32) or `dtype`, rows a_token apart.
+ * q, k [T, key_heads, dk] (head h reads key head h / (heads / key_heads)), v [T, heads, dv], beta [T, heads] rows b_token apart:
+ * views in `dtype`, strides in elements.  seq_info, state slots and out as for tlb_decay_scan.  dk <= 256. */
+int tlb_delta_scan(const void *q, long long q_token, long long q_head, const void *k, long long k_token, long long k_head, const void *v,
+                   long long v_token, long long v_head, const void *beta, long long b_token, const void *a, int a_is_f32, long long a_token,
+                   int per_channel, const void *a_log, const void *dt_bias, float q_scale, float unit_eps, int heads, int key_heads, int dk, int dv,
+                   const int32_t *seq_info, int num_seqs, float *state, long long slot_stride, int num_slots, float *out, int dtype, void *stream);
+/* Short causal convolution along every sequence, per channel: y[t, c] = act(sum_i taps[c, K-1-i] x[t-i, c]) (act 1 = silu,
+ * 0 = none), zeros before position 0.  x [T, channels] rows x_token apart, taps [channels, K] (K <= 8), y [T, channels]
+ * contiguous.  The K-1 inputs before a step's first token live in the sequence's state slot (state + slot * slot_stride
+ * floats, [channels, K-1], oldest first) and are replaced by the step's last ones. */
+int tlb_short_conv(const void *x, long long x_token, const void *taps, int channels, int num_taps, int act, const int32_t *seq_info, int num_seqs,
+                   int max_tokens_per_seq, float *state, long long slot_stride, int num_slots, void *y, int dtype, void *stream);
+
+/* out = act(x) elementwise over [rows, width]; act 0 = silu, 1 = gelu (tanh form), 2 = squared relu. */
+int tlb_act_rows(const void *x, void *out, int rows, int width, int act, int dtype, void *stream);
+/* x <- cap * tanh(x / cap), fp32 [rows, width] in place. */
+int tlb_softcap_rows(float *x, int rows, int width, float cap, void *stream);
+/* dst[r, 0:dim] = src[r, :] rounded to `dtype`; dst rows dst_stride elements apart. */
+int tlb_cast_rows(const float *src, void *dst, long long dst_stride, int rows, int dim, int dtype, void *stream);
 
 /* out[t, j] = act(gu[t, j]) * gu[t, width + j]; act 0 = silu, 1 = gelu (tanh form). */
 int tlb_gated_act(const void *gu, void *out, int rows, int width, int act, int dtype, void *stream);
 
 /* Router: logits = W h + b in fp32 (h, W, b stored in `dtype`; b may be NULL), the `top` largest per token (lower index
  * wins a tie).  scoring 0: weights = softmax over the chosen logits; 1: weights = sigmoid of each chosen logit, not
- * renormalised.  idx [tokens, top] int32, gate [tokens, top] fp32. */
-int tlb_moe_route(const void *h, const void *w, const void *b, int tokens, int dim, int experts, int top, int scoring, int32_t *idx,
-                  float *gate, int dtype, void *stream);
+ * renormalised; 2: scores = softmax over ALL logits, the choice is made by score + choice_bias (`dtype` [experts] or NULL),
+ * weights = the chosen scores / (their sum + 1e-20) * weight_scale.  idx [tokens, top] int32, gate [tokens, top] fp32. */
+int tlb_moe_route(const void *h, const void *w, const void *b, int tokens, int dim, int experts, int top, int scoring, const void *choice_bias,
+                  float weight_scale, int32_t *idx, float *gate, int dtype, void *stream);
 
 /* Rows per expert tile of the grouped products: 32, or 64 for the tensor-core kernels (bf16, reduction length % 8 == 0)
  * when experts get many rows (half the weight traffic per row). */
@@ -179,9 +214,11 @@ int tlb_moe_scale_rows(const void *h, const float *gate, void *out, int tokens, 
 int tlb_moe_down(const void *inter, const void *wd, const int32_t *sorted_pair, const int32_t *tile_expert, const int32_t *counters,
                  int tokens, int top, int experts, int tile_rows, int dim, int ff, float *pair_out, int dtype, void *stream);
 /* y[t,:] = sum_k gate[t,k] * pair_out[t*top+k,:] (+ shared[t,:] if shared != NULL, stored in `dtype`), fp32, in choice order;
- * gate == NULL: every weight is 1. */
-int tlb_moe_combine(const float *pair_out, const float *gate, const void *shared, float *y, int tokens, int top, int dim, int dtype,
-                    void *stream);
+ * gate == NULL: every weight is 1.  idx != NULL: a choice with idx[t,k] >= experts is an identity expert (the router has
+ * more outputs than there are experts): its output is the token's input h[t,:] (`dtype`), and the grouped products, given
+ * `experts` as their count, skip it. */
+int tlb_moe_combine(const float *pair_out, const float *gate, const void *shared, const int32_t *idx, int experts, const void *h, float *y,
+                    int tokens, int top, int dim, int dtype, void *stream);
 
 /* Row-wise arg-max of fp32 logits [rows, vocab] (lowest index wins a tie). */
 int tlb_argmax_rows(const float *logits, int32_t *out, int rows, int vocab, void *stream);

@@ -45,7 +45,9 @@ template <typename T, int KR /* rows per lane: dk <= 4 * KR */, int kLaTokens /*
 __global__ void __launch_bounds__(kLaCols * kLaLanes)
 decay_scan_kernel(const T *__restrict__ q, long long q_token, long long q_head, const T *__restrict__ k, long long k_token, long long k_head,
                   const T *__restrict__ v, long long v_token, long long v_head, const float *__restrict__ z, long long z_token,
-                  const T *__restrict__ z_bias, float inv_tau, float q_scale, int heads, int dk, int dv, const int32_t *__restrict__ seq_info,
+                  const T *__restrict__ z_bias, float inv_tau, const float *__restrict__ head_decay, const float *__restrict__ rope_cos,
+                  const float *__restrict__ rope_sin, int rope_dims, int rope_interleaved, float q_scale, int heads, int dk, int dv,
+                  const int32_t *__restrict__ seq_info,
                   float *__restrict__ state, long long slot_stride, int num_slots, float *__restrict__ out, int pass, int max_segments,
                   float *__restrict__ seg_state, float *__restrict__ seg_decay) {
     __shared__ float4 sx[kLaTokens * 4 * KR];  // per token and key channel: (decay, k, scaled q, -), one 16-byte read per row
@@ -83,9 +85,21 @@ decay_scan_kernel(const T *__restrict__ q, long long q_token, long long q_head, 
         for (int e = threadIdx.x; e < n * dk; e += blockDim.x) {
             int j = e / dk, d = e - j * dk;
             size_t tok = (size_t)(first + t0 + j);
-            float logit = z[tok * z_token + (size_t)head * dk + d] + (z_bias ? to_f(z_bias[(size_t)head * dk + d]) : 0.f);
-            sx[j * 4 * KR + d] = make_float4(expf(log_sigmoid(logit) * inv_tau), to_f(k[tok * k_token + (size_t)head * k_head + d]),
-                                             to_f(q[tok * q_token + (size_t)head * q_head + d]) * q_scale, 0.f);
+            float alpha;
+            if (head_decay) alpha = head_decay[head];
+            else alpha = expf(log_sigmoid(z[tok * z_token + (size_t)head * dk + d] + (z_bias ? to_f(z_bias[(size_t)head * dk + d]) : 0.f)) * inv_tau);
+            const T *kp = k + tok * k_token + (size_t)head * k_head, *qp = q + tok * q_token + (size_t)head * q_head;
+            float kd = to_f(kp[d]), qd = to_f(qp[d]);
+            if (d < rope_dims) {  // rotate the pair this entry belongs to, in fp32, by the token's tabulated angle
+                const int half = rope_dims >> 1;
+                const bool low = rope_interleaved ? !(d & 1) : d < half;
+                const int i = rope_interleaved ? d >> 1 : (low ? d : d - half);
+                const int other = rope_interleaved ? (d ^ 1) : (low ? d + half : d - half);
+                const float c = rope_cos[tok * half + i], sn = low ? -rope_sin[tok * half + i] : rope_sin[tok * half + i];
+                kd = kd * c + to_f(kp[other]) * sn;
+                qd = qd * c + to_f(qp[other]) * sn;
+            }
+            sx[j * 4 * KR + d] = make_float4(alpha, kd, qd * q_scale, 0.f);
         }
         for (int e = threadIdx.x; e < n * kLaCols; e += blockDim.x) {
             int j = e / kLaCols, d = e - j * kLaCols;
@@ -165,7 +179,8 @@ decay_combine_kernel(const int32_t *__restrict__ seq_info, const float *__restri
     }
 }
 
-// out[t, h, :] = o[t, h, :] / rms(o[t, h, :]) * w * act(gate[t, h, :]); one warp per (token, head).  act 0 = none, 1 = silu.
+// out[t, h, :] = o[t, h, :] / rms(o[t, h, :]) * w * act(gate[t, h, :]); one warp per (token, head).  act 0 = none, 1 = silu,
+// 2 = sigmoid; w == NULL: no weight.
 template <typename T>
 __global__ void __launch_bounds__(128)
 head_norm_gate_kernel(const float *__restrict__ o, const T *__restrict__ w, float eps, const T *__restrict__ gate, long long g_token, int act,
@@ -181,10 +196,10 @@ head_norm_gate_kernel(const float *__restrict__ o, const T *__restrict__ w, floa
     ss = warp_sum(ss);
     float inv = 1.0f / sqrtf(ss / (float)dv + eps);
     for (int d = lane; d < dv; d += 32) {
-        float y = src[d] * inv * to_f(w[d]);
+        float y = src[d] * inv * (w ? to_f(w[d]) : 1.f);
         if (gate) {
             float gv = to_f(gate[(size_t)t * g_token + (size_t)head * dv + d]);
-            y *= act == 1 ? gv / (1.0f + expf(-gv)) : gv;
+            y *= act == 1 ? gv / (1.0f + expf(-gv)) : act == 2 ? 1.0f / (1.0f + expf(-gv)) : gv;
         }
         out[(size_t)row * dv + d] = from_f<T>(y);
     }
@@ -203,13 +218,16 @@ size_t tlb_decay_scan_workspace(int num_seqs, int max_tokens_per_seq, int heads,
 }
 
 int tlb_decay_scan(const void *q, long long q_token, long long q_head, const void *k, long long k_token, long long k_head, const void *v,
-                   long long v_token, long long v_head, const float *z, long long z_token, const void *z_bias, float tau, float q_scale, int heads,
+                   long long v_token, long long v_head, const float *z, long long z_token, const void *z_bias, float tau, const float *head_decay,
+                   const float *rope_cos, const float *rope_sin, int rope_dims, int rope_interleaved, float q_scale, int heads,
                    int dk, int dv, const int32_t *seq_info, int num_seqs, int max_tokens_per_seq, float *state, long long slot_stride, int num_slots,
                    float *out, void *workspace, size_t workspace_bytes, int dtype, void *stream) {
     if (num_seqs <= 0) return TL_OK;
-    if (!q || !k || !v || !z || !seq_info || !state || !out || heads <= 0 || dk <= 0 || dv <= 0 || !(tau > 0.f) || num_slots <= 0 ||
-        max_tokens_per_seq <= 0)
+    if (!q || !k || !v || (!z && !head_decay) || !seq_info || !state || !out || heads <= 0 || dk <= 0 || dv <= 0 || (z && !(tau > 0.f)) ||
+        num_slots <= 0 || max_tokens_per_seq <= 0)
         return tl::fail(TL_EINVAL, "decay_scan: bad argument");
+    if (rope_dims < 0 || (rope_dims & 1) || rope_dims > dk || (rope_dims > 0 && (!rope_cos || !rope_sin)))
+        return tl::fail(TL_EINVAL, "decay_scan: bad rotation of %d of %d entries", rope_dims, dk);
     if (dk > 256) return tl::fail(TL_EINVAL, "decay_scan: key size %d > 256", dk);
     // portions longer than a segment are cut at absolute multiples of the segment length and run in three passes
     const bool segmented = max_tokens_per_seq > kLaSegment;
@@ -226,8 +244,8 @@ int tlb_decay_scan(const void *q, long long q_token, long long q_head, const voi
     int kr = ceil_div(dk, kLaLanes);
 #define TLB_DS_K(KRV, PASS, GZ)                                                                                                                    \
     decay_scan_kernel<T, KRV, (KRV > 32 ? 8 : 16)><<<dim3(num_seqs, heads * colblocks, GZ), kLaCols * kLaLanes, 0, st>>>(                                                \
-        (const T *)q, q_token, q_head, (const T *)k, k_token, k_head, (const T *)v, v_token, v_head, z, z_token, (const T *)z_bias, 1.0f / tau, q_scale, \
-        heads, dk, dv, seq_info, state, slot_stride, num_slots, out, PASS, max_segments, seg_state, seg_decay)
+        (const T *)q, q_token, q_head, (const T *)k, k_token, k_head, (const T *)v, v_token, v_head, z, z_token, (const T *)z_bias, z ? 1.0f / tau : 0.f, head_decay, \
+        rope_cos, rope_sin, rope_dims, rope_interleaved, q_scale, heads, dk, dv, seq_info, state, slot_stride, num_slots, out, PASS, max_segments, seg_state, seg_decay)
 #define TLB_DS(PASS, GZ) TLB_DISPATCH(dtype, "decay_scan", if (kr <= 8) TLB_DS_K(8, PASS, GZ); else if (kr <= 16) TLB_DS_K(16, PASS, GZ); else if (kr <= 32) TLB_DS_K(32, PASS, GZ); else TLB_DS_K(64, PASS, GZ))
     if (!segmented) {
         TLB_DS(0, 1);
@@ -249,7 +267,7 @@ int tlb_decay_scan(const void *q, long long q_token, long long q_head, const voi
 int tlb_head_norm_gate(const float *o, const void *w, float eps, const void *gate, long long g_token, int act, void *out, int tokens, int heads,
                        int dv, int dtype, void *stream) {
     if (tokens <= 0) return TL_OK;
-    if (!o || !w || !out || heads <= 0 || dv <= 0 || act < 0 || act > 1) return tl::fail(TL_EINVAL, "head_norm_gate: bad argument");
+    if (!o || !out || heads <= 0 || dv <= 0 || act < 0 || act > 2) return tl::fail(TL_EINVAL, "head_norm_gate: bad argument");
     long long rows = (long long)tokens * heads;
     TLB_DISPATCH(dtype, "head_norm_gate",
                  head_norm_gate_kernel<T><<<(unsigned)((rows + 3) / 4), 128, 0, as_stream(stream)>>>(o, (const T *)w, eps, (const T *)gate, g_token, act,

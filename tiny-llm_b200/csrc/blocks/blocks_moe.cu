@@ -30,10 +30,11 @@ __device__ __forceinline__ int moe_src_row(int pair, int sorted_row, int top, in
 template <typename T>
 __global__ void __launch_bounds__(256)
 moe_route_kernel(const T *__restrict__ h, const T *__restrict__ w, const T *__restrict__ b, int tokens, int dim, int experts, int top, int scoring,
-                 int32_t *__restrict__ idx, float *__restrict__ gate) {
+                 const T *__restrict__ choice_bias, float weight_scale, int32_t *__restrict__ idx, float *__restrict__ gate) {
     extern __shared__ float route_smem[];
     float *x = route_smem;        // [dim]
-    float *z = route_smem + dim;  // [experts]
+    float *z = route_smem + dim;  // [experts]: what the choice is made by
+    float *p_all = z + experts;   // [experts]: scoring 2, the softmax over all outputs
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
     for (int d = threadIdx.x; d < dim; d += blockDim.x) x[d] = to_f(h[(size_t)t * dim + d]);
@@ -47,6 +48,19 @@ moe_route_kernel(const T *__restrict__ h, const T *__restrict__ w, const T *__re
     }
     __syncthreads();
     if (warp != 0) return;
+    if (scoring == 2) {  // scores = softmax over ALL outputs; the choice adds a bias to them, the weights do not
+        float m = -INFINITY, sum = 0.f;
+        for (int e = lane; e < experts; e += 32) m = fmaxf(m, z[e]);
+        m = warp_max(m);
+        for (int e = lane; e < experts; e += 32) sum += expf(z[e] - m);
+        sum = warp_sum(sum);
+        for (int e = lane; e < experts; e += 32) {
+            float p = expf(z[e] - m) / sum;
+            p_all[e] = p;
+            z[e] = p + (choice_bias ? to_f(choice_bias[e]) : 0.f);
+        }
+        __syncwarp();
+    }
     // top-k by repeated arg-max over the warp (lower index wins a tie); weights = softmax over the chosen logits
     float first_v = 0.f, denom = 0.f;
     for (int k = 0; k < top; ++k) {
@@ -63,7 +77,7 @@ moe_route_kernel(const T *__restrict__ h, const T *__restrict__ w, const T *__re
         }
         if (k == 0) first_v = bv;
         // scoring 0: softmax over the chosen logits (the first choice is the largest); 1: each choice's own sigmoid, as it is
-        float p = scoring == 1 ? 1.0f / (1.0f + expf(-bv)) : expf(bv - first_v);
+        float p = scoring == 1 ? 1.0f / (1.0f + expf(-bv)) : scoring == 2 ? p_all[min(bi, experts - 1)] : expf(bv - first_v);
         denom += p;
         if (lane == 0) {
             idx[(size_t)t * top + k] = bi;
@@ -73,7 +87,9 @@ moe_route_kernel(const T *__restrict__ h, const T *__restrict__ w, const T *__re
         __syncwarp();
     }
     if (scoring == 1) return;
-    for (int k = lane; k < top; k += 32) gate[(size_t)t * top + k] /= denom;
+    // scoring 2: the chosen scores renormalised (a guard against an all-zero choice) and scaled
+    for (int k = lane; k < top; k += 32)
+        gate[(size_t)t * top + k] = scoring == 2 ? gate[(size_t)t * top + k] / (denom + 1e-20f) * weight_scale : gate[(size_t)t * top + k] / denom;
 }
 
 // Single CTA: histogram, padded exclusive scan, scatter.
@@ -302,13 +318,17 @@ __global__ void moe_scale_rows_kernel(const T *__restrict__ h, const float *__re
     for (int d = threadIdx.x; d < dim; d += blockDim.x) out[(size_t)pair * dim + d] = from_f<T>(g * to_f(src[d]));
 }
 
+// idx != NULL: a choice whose expert id is >= experts is an identity expert, its output the token's input row h[t, :].
 template <typename T>
 __global__ void moe_combine_kernel(const float *__restrict__ pair_out, const float *__restrict__ gate, const T *__restrict__ shared,
-                                   float *__restrict__ y, int top, int dim) {
+                                   const int32_t *__restrict__ idx, int experts, const T *__restrict__ h, float *__restrict__ y, int top, int dim) {
     int t = blockIdx.x;
     for (int d = threadIdx.x; d < dim; d += blockDim.x) {
         float s = 0.f;
-        for (int k = 0; k < top; ++k) s = fmaf(gate ? gate[(size_t)t * top + k] : 1.f, pair_out[((size_t)t * top + k) * dim + d], s);
+        for (int k = 0; k < top; ++k) {
+            const bool same = idx != nullptr && idx[(size_t)t * top + k] >= experts;
+            s = fmaf(gate ? gate[(size_t)t * top + k] : 1.f, same ? to_f(h[(size_t)t * dim + d]) : pair_out[((size_t)t * top + k) * dim + d], s);
+        }
         if (shared) s += to_f(shared[(size_t)t * dim + d]);
         y[(size_t)t * dim + d] = s;
     }
@@ -338,16 +358,16 @@ static bool moe_mma_ok(int dtype, int k, const void *a, const void *w1, const vo
 
 extern "C" {
 
-int tlb_moe_route(const void *h, const void *w, const void *b, int tokens, int dim, int experts, int top, int scoring, int32_t *idx, float *gate,
-                  int dtype, void *stream) {
+int tlb_moe_route(const void *h, const void *w, const void *b, int tokens, int dim, int experts, int top, int scoring, const void *choice_bias,
+                  float weight_scale, int32_t *idx, float *gate, int dtype, void *stream) {
     if (tokens <= 0) return TL_OK;
-    if (!h || !w || !idx || !gate || dim <= 0 || experts <= 0 || top <= 0 || top > experts || scoring < 0 || scoring > 1)
+    if (!h || !w || !idx || !gate || dim <= 0 || experts <= 0 || top <= 0 || top > experts || scoring < 0 || scoring > 2)
         return tl::fail(TL_EINVAL, "moe_route: bad argument");
-    size_t smem = ((size_t)dim + experts) * sizeof(float);
+    size_t smem = ((size_t)dim + 2 * (size_t)experts) * sizeof(float);
     if (smem > 48 * 1024) return tl::fail(TL_EINVAL, "moe_route: width %d + %d experts do not fit", dim, experts);
     TLB_DISPATCH(dtype, "moe_route",
                  moe_route_kernel<T><<<tokens, 256, smem, as_stream(stream)>>>((const T *)h, (const T *)w, (const T *)b, tokens, dim, experts, top, scoring,
-                                                                             idx, gate));
+                                                                             (const T *)choice_bias, weight_scale, idx, gate));
     TL_LAUNCH_CHECK("moe_route");
     return TL_OK;
 }
@@ -458,11 +478,12 @@ int tlb_moe_down(const void *inter, const void *wd, const int32_t *sorted_pair, 
     return TL_OK;
 }
 
-int tlb_moe_combine(const float *pair_out, const float *gate, const void *shared, float *y, int tokens, int top, int dim, int dtype, void *stream) {
+int tlb_moe_combine(const float *pair_out, const float *gate, const void *shared, const int32_t *idx, int experts, const void *h, float *y, int tokens,
+                    int top, int dim, int dtype, void *stream) {
     if (tokens <= 0) return TL_OK;
-    if (!pair_out || !y || top <= 0 || dim <= 0) return tl::fail(TL_EINVAL, "moe_combine: bad argument");
+    if (!pair_out || !y || top <= 0 || dim <= 0 || (idx && !h)) return tl::fail(TL_EINVAL, "moe_combine: bad argument");
     TLB_DISPATCH(dtype, "moe_combine",
-                 moe_combine_kernel<T><<<tokens, 256, 0, as_stream(stream)>>>(pair_out, gate, (const T *)shared, y, top, dim));
+                 moe_combine_kernel<T><<<tokens, 256, 0, as_stream(stream)>>>(pair_out, gate, (const T *)shared, idx, experts, (const T *)h, y, top, dim));
     TL_LAUNCH_CHECK("moe_combine");
     return TL_OK;
 }

@@ -121,16 +121,17 @@ __global__ void norm_residual_kernel(const TY *__restrict__ y, const T *__restri
 }
 
 
-// residual += a (+ b) in fp32, then (w != NULL) h = residual / rms(residual) * w rounded to T: the end of a layer whose
-// sublayers both read one norm of the stream, fused with the next layer's norm.
+// residual += a (+ b) in fp32, then (w != NULL) h = residual / rms(residual) * w rounded to T: the end of a sublayer (or of
+// a layer whose sublayers both read one norm of the stream), fused with the norm that reads the stream next.  a_row: `a`
+// is ONE row [dim] added to every row (a learned offset).
 template <typename T>
-__global__ void add_norm_kernel(float *__restrict__ residual, const float *__restrict__ a, const float *__restrict__ b, const T *__restrict__ w,
-                                float eps, T *__restrict__ h, int dim) {
+__global__ void add_norm_kernel(float *__restrict__ residual, const float *__restrict__ a, int a_row, const float *__restrict__ b,
+                                const T *__restrict__ w, float eps, T *__restrict__ h, int dim) {
     __shared__ float scratch[33];
-    size_t base = (size_t)blockIdx.x * dim;
+    size_t base = (size_t)blockIdx.x * dim, abase = a_row ? 0 : base;
     float ss = 0.f;
     for (int d = threadIdx.x; d < dim; d += blockDim.x) {
-        float x = residual[base + d] + (b ? a[base + d] + b[base + d] : a[base + d]);
+        float x = residual[base + d] + (b ? a[abase + d] + b[base + d] : a[abase + d]);
         residual[base + d] = x;
         ss += x * x;
     }
@@ -161,13 +162,18 @@ __global__ void norm_mix2_kernel(const float *__restrict__ a, const T *__restric
 
 template <typename T>
 __global__ void rope_rows_kernel(T *x, long long row_stride, long long head_stride, int first, int heads, int dims, int interleaved,
-                                 double log2_base, const int32_t *__restrict__ tok_pos) {
+                                 double log2_base, double inv_factor, const int32_t *__restrict__ tok_pos) {
     int row = blockIdx.x;
     int pos = tok_pos[row];
     int half = dims / 2;
     for (int i = threadIdx.x; i < half; i += blockDim.x) {
         float c, s;
-        rope_angle(pos, i, dims, log2_base, c, s);
+        if (inv_factor == 1.0) rope_angle(pos, i, dims, log2_base, c, s);
+        else {  // linear scaling: every frequency divided by the factor
+            double sn, cs;
+            sincos((double)pos * exp2(-2.0 * (double)i / (double)dims * log2_base) * inv_factor, &sn, &cs);
+            c = (float)cs, s = (float)sn;
+        }
         int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + half;
         for (int hd = 0; hd < heads; ++hd) {
             T *p = x + (size_t)row * row_stride + (size_t)hd * head_stride + first;
@@ -231,6 +237,29 @@ __device__ __forceinline__ float act_apply(float z, int act) {
     return 0.5f * z * (1.0f + tanhf(inner));
 }
 
+// out = act(x) elementwise; act 0 = silu, 1 = gelu (tanh form), 2 = squared relu.
+template <typename T>
+__global__ void act_rows_kernel(const T *__restrict__ x, T *__restrict__ out, long long total, int act) {
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    float z = to_f(x[i]);
+    out[i] = from_f<T>(act == 2 ? (z > 0.f ? z * z : 0.f) : act_apply(z, act));
+}
+
+// x <- cap * tanh(x / cap), fp32 in place.
+__global__ void softcap_rows_kernel(float *__restrict__ x, long long total, float cap) {
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) x[i] = cap * tanhf(x[i] / cap);
+}
+
+// dst[r, :] = src[r, :] rounded to T; dst rows dst_stride elements apart (a column block of a wider matrix).
+template <typename T>
+__global__ void cast_rows_kernel(const float *__restrict__ src, T *__restrict__ dst, long long dst_stride, int dim) {
+    const float *s = src + (size_t)blockIdx.x * dim;
+    T *d = dst + (size_t)blockIdx.x * dst_stride;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) d[i] = from_f<T>(s[i]);
+}
+
 template <typename T>
 __global__ void gated_act_kernel(const T *__restrict__ gu, T *__restrict__ out, long long total, int width, int act) {
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -278,7 +307,7 @@ using namespace tlb;
 
 extern "C" {
 
-int tlb_abi_version(void) { return 3; }
+int tlb_abi_version(void) { return 4; }
 const char *tlb_last_error(void) { return tl::g_error; }
 long long tlb_launch_count(void) { return tl::g_launches.load(std::memory_order_relaxed); }
 
@@ -309,11 +338,12 @@ int tlb_norm_residual(const void *y, int y_is_f32, const void *w, float weight_o
     return TL_OK;
 }
 
-int tlb_add_norm(float *residual, const float *a, const float *b, const void *w, float eps, void *h, int rows, int dim, int dtype, void *stream) {
+int tlb_add_norm(float *residual, const float *a, int a_row, const float *b, const void *w, float eps, void *h, int rows, int dim, int dtype,
+                 void *stream) {
     if (rows <= 0) return TL_OK;
     if (!residual || !a || dim <= 0 || ((w == nullptr) != (h == nullptr))) return tl::fail(TL_EINVAL, "add_norm: bad argument");
     int threads = dim >= 2048 ? 256 : 128;
-    TLB_DISPATCH(dtype, "add_norm", add_norm_kernel<T><<<rows, threads, 0, as_stream(stream)>>>(residual, a, b, (const T *)w, eps, (T *)h, dim));
+    TLB_DISPATCH(dtype, "add_norm", add_norm_kernel<T><<<rows, threads, 0, as_stream(stream)>>>(residual, a, a_row, b, (const T *)w, eps, (T *)h, dim));
     TL_LAUNCH_CHECK("add_norm");
     return TL_OK;
 }
@@ -330,12 +360,12 @@ int tlb_norm_mix2(const float *a, const void *wa, const float *b, const void *wb
 }
 
 int tlb_rope_rows(void *x, long long row_stride, long long head_stride, int first, int heads, int dims, int interleaved, double base,
-                  const int32_t *tok_pos, int rows, int dtype, void *stream) {
+                  double factor, const int32_t *tok_pos, int rows, int dtype, void *stream) {
     if (rows <= 0 || dims <= 0) return TL_OK;
-    if (!x || !tok_pos || heads <= 0 || (dims & 1) || base <= 0) return tl::fail(TL_EINVAL, "rope_rows: bad argument");
+    if (!x || !tok_pos || heads <= 0 || (dims & 1) || base <= 0 || !(factor > 0)) return tl::fail(TL_EINVAL, "rope_rows: bad argument");
     double lb = log2(base);
     TLB_DISPATCH(dtype, "rope_rows",
-                 rope_rows_kernel<T><<<rows, 64, 0, as_stream(stream)>>>((T *)x, row_stride, head_stride, first, heads, dims, interleaved, lb, tok_pos));
+                 rope_rows_kernel<T><<<rows, 64, 0, as_stream(stream)>>>((T *)x, row_stride, head_stride, first, heads, dims, interleaved, lb, 1.0 / factor, tok_pos));
     TL_LAUNCH_CHECK("rope_rows");
     return TL_OK;
 }
@@ -373,6 +403,32 @@ int tlb_gated_act(const void *gu, void *out, int rows, int width, int act, int d
     TLB_DISPATCH(dtype, "gated_act",
                  gated_act_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, as_stream(stream)>>>((const T *)gu, (T *)out, total, width, act));
     TL_LAUNCH_CHECK("gated_act");
+    return TL_OK;
+}
+
+int tlb_act_rows(const void *x, void *out, int rows, int width, int act, int dtype, void *stream) {
+    if (rows <= 0 || width <= 0) return TL_OK;
+    if (!x || !out || act < 0 || act > 2) return tl::fail(TL_EINVAL, "act_rows: bad argument");
+    long long total = (long long)rows * width;
+    TLB_DISPATCH(dtype, "act_rows", act_rows_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, as_stream(stream)>>>((const T *)x, (T *)out, total, act));
+    TL_LAUNCH_CHECK("act_rows");
+    return TL_OK;
+}
+
+int tlb_softcap_rows(float *x, int rows, int width, float cap, void *stream) {
+    if (rows <= 0 || width <= 0) return TL_OK;
+    if (!x || !(cap > 0.f)) return tl::fail(TL_EINVAL, "softcap_rows: bad argument");
+    long long total = (long long)rows * width;
+    softcap_rows_kernel<<<(unsigned)((total + 255) / 256), 256, 0, as_stream(stream)>>>(x, total, cap);
+    TL_LAUNCH_CHECK("softcap_rows");
+    return TL_OK;
+}
+
+int tlb_cast_rows(const float *src, void *dst, long long dst_stride, int rows, int dim, int dtype, void *stream) {
+    if (rows <= 0 || dim <= 0) return TL_OK;
+    if (!src || !dst || dst_stride < dim) return tl::fail(TL_EINVAL, "cast_rows: bad argument");
+    TLB_DISPATCH(dtype, "cast_rows", cast_rows_kernel<T><<<rows, 128, 0, as_stream(stream)>>>(src, (T *)dst, dst_stride, dim));
+    TL_LAUNCH_CHECK("cast_rows");
     return TL_OK;
 }
 

@@ -49,6 +49,7 @@ BLOCKS_SOURCES = [
     "blocks/blocks_paged_attention.cu",
     "blocks/blocks_paged_attention_mma.cu",
     "blocks/blocks_linear_attention.cu",
+    "blocks/blocks_delta_rule.cu",
 ]
 
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")

@@ -26,7 +26,8 @@ _SIGNATURES = {
     "tlb_launch_count": (_LL, []),
     "tlb_embed_rows": (_I, [_VP, _VP, _VP, _VP, _I, _I, _I, _I, _VP]),
     "tlb_norm_residual": (_I, [_VP, _I, _VP, _F, _VP, _F, _VP, _VP, _I, _I, _I, _VP]),
-    "tlb_rope_rows": (_I, [_VP, _LL, _LL, _I, _I, _I, _I, _D, _VP, _I, _I, _VP]),
+    "tlb_rope_rows": (_I, [_VP, _LL, _LL, _I, _I, _I, _I, _D, _D, _VP, _I, _I, _VP]),
+    "tlb_rope_table": (_I, [_VP, _I, _I, _D, _D, _VP, _VP, _VP]),
     "tlb_latent_append": (_I, [_VP, _VP, _F, _I, _I, _I, _I, _D, _VP, _VP, _VP, _I, _I, _I, _VP, _I, _I, _VP]),
     "tlb_latent_prepare": (_I, [_VP, _LL, _VP, _F, _I, _I, _I, _I, _D, _VP, _VP, _VP, _I, _I, _I, _VP, _VP, _LL, _I, _I, _I, _I, _I, _VP]),
     "tlb_latent_attention": (_I, [_VP, _LL, _LL, _VP, _LL, _LL, _VP, _I, _I, _I, _I, _VP, _I, _VP, _I, _VP, _I, _I, _F, _VP, _LL, _LL, _I, _VP]),
@@ -36,10 +37,10 @@ _SIGNATURES = {
                                       ctypes.c_size_t, _VP]),
     "tlb_latent_attention_mma_workspace": (ctypes.c_size_t, [_I, _I, _I, _I]),
     "tlb_gated_act": (_I, [_VP, _VP, _I, _I, _I, _I, _VP]),
-    "tlb_moe_route": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _VP, _VP, _I, _VP]),
+    "tlb_moe_route": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _VP, _F, _VP, _VP, _I, _VP]),
     "tlb_moe_up": (_I, [_VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _I, _I, _VP, _I, _VP]),
     "tlb_moe_scale_rows": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _VP]),
-    "tlb_add_norm": (_I, [_VP, _VP, _VP, _VP, _F, _VP, _I, _I, _I, _VP]),
+    "tlb_add_norm": (_I, [_VP, _VP, _I, _VP, _VP, _F, _VP, _I, _I, _I, _VP]),
     "tlb_norm_mix2": (_I, [_VP, _VP, _VP, _VP, _F, _F, _VP, _I, _I, _I, _VP]),
     "tlb_paged_attention_tile_tokens": (_I, [_I, _I]),
     "tlb_paged_attention": (_I, [_VP, _LL, _LL, _VP, _I, _I, _I, _I, _I, _I, _VP, _I, _VP, _I, _VP, _I, _I, _F, _F, _I, _VP, _LL, _VP, _LL, _LL, _I, _VP]),
@@ -50,24 +51,30 @@ _SIGNATURES = {
     "tlb_paged_attention_mma_workspace": (ctypes.c_size_t, [_I, _I, _I, _I, _I]),
     "tlb_kv_prepare": (_I, [_VP, _LL, _LL, _I, _VP, _VP, _LL, _LL, _VP, _LL, _LL, _I, _I, _I, _VP, _F, _VP, _VP, _VP, _I, _I, _I, _VP, _I, _I, _VP]),
     "tlb_decay_scan_workspace": (ctypes.c_size_t, [_I, _I, _I, _I, _I]),
-    "tlb_decay_scan": (_I, [_VP, _LL, _LL, _VP, _LL, _LL, _VP, _LL, _LL, _VP, _LL, _VP, _F, _F, _I, _I, _I, _VP, _I, _I, _VP, _LL, _I, _VP, _VP, ctypes.c_size_t,
-                            _I, _VP]),
+    "tlb_decay_scan": (_I, [_VP, _LL, _LL, _VP, _LL, _LL, _VP, _LL, _LL, _VP, _LL, _VP, _F, _VP, _VP, _VP, _I, _I, _F, _I, _I, _I, _VP, _I, _I, _VP, _LL, _I,
+                            _VP, _VP, ctypes.c_size_t, _I, _VP]),
+    "tlb_delta_scan": (_I, [_VP, _LL, _LL, _VP, _LL, _LL, _VP, _LL, _LL, _VP, _LL, _VP, _I, _LL, _I, _VP, _VP, _F, _F, _I, _I, _I, _I, _VP, _I, _VP, _LL, _I,
+                            _VP, _I, _VP]),
+    "tlb_short_conv": (_I, [_VP, _LL, _VP, _I, _I, _I, _VP, _I, _I, _VP, _LL, _I, _VP, _I, _VP]),
+    "tlb_act_rows": (_I, [_VP, _VP, _I, _I, _I, _I, _VP]),
+    "tlb_softcap_rows": (_I, [_VP, _I, _I, _F, _VP]),
+    "tlb_cast_rows": (_I, [_VP, _VP, _LL, _I, _I, _I, _VP]),
     "tlb_head_norm_gate": (_I, [_VP, _VP, _F, _VP, _LL, _I, _VP, _I, _I, _I, _I, _VP]),
     "tlb_moe_max_rows": (_LL, [_I, _I, _I, _I]),
     "tlb_moe_sort": (_I, [_VP, _I, _I, _I, _I, _VP, _VP, _VP, _VP]),
     "tlb_moe_gate_up": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _I, _VP, _I, _VP]),
     "tlb_moe_down": (_I, [_VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _VP, _I, _VP]),
-    "tlb_moe_combine": (_I, [_VP, _VP, _VP, _VP, _I, _I, _I, _I, _VP]),
+    "tlb_moe_combine": (_I, [_VP, _VP, _VP, _VP, _I, _VP, _VP, _I, _I, _I, _I, _VP]),
     "tlb_argmax_rows": (_I, [_VP, _VP, _I, _I, _VP]),
 }
 EXPORTED_SYMBOLS = tuple(_SIGNATURES)
 
-ABI_VERSION = 3
+ABI_VERSION = 4
 ATTENTION_TILE_TOKENS = 4
 MOE_TILE_ROWS = 32
 ACT_SILU, ACT_GELU_TANH, ACT_RELU_SQUARED = 0, 1, 2
 MASK_CAUSAL, MASK_WINDOW, MASK_CHUNK = 0, 1, 2
-SCORE_SOFTMAX, SCORE_SIGMOID = 0, 1
+SCORE_SOFTMAX, SCORE_SIGMOID, SCORE_SOFTMAX_ALL = 0, 1, 2
 _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 2}
 
 
@@ -185,16 +192,30 @@ def norm_residual(y, weight, eps: float, *, weight_offset: float = 0.0, scale=No
     return h
 
 
-def rope_rows(x: torch.Tensor, tok_pos: torch.Tensor, *, heads: int, head_stride: int, first: int, dims: int, base: float, interleaved: bool):
-    """Rotate, in place, ``dims`` entries from ``first`` in each of ``heads`` heads of every row of ``x [rows, *]``."""
+def rope_rows(x: torch.Tensor, tok_pos: torch.Tensor, *, heads: int, head_stride: int, first: int, dims: int, base: float, interleaved: bool,
+              factor: float = 1.0):
+    """Rotate, in place, ``dims`` entries from ``first`` in each of ``heads`` heads of every row of ``x [rows, *]``;
+    ``factor`` divides every frequency (linear scaling of the positions)."""
     _gpu("rope_rows", x, tok_pos)
     if x.dim() != 2 or x.stride(1) != 1 or tok_pos.dtype != torch.int32 or tok_pos.numel() != x.shape[0]:
         raise RuntimeError("rope_rows: x must be [rows, n] with unit inner stride and tok_pos int32 [rows]")
     if first + dims > head_stride or (heads - 1) * head_stride + first + dims > x.shape[1]:
         raise RuntimeError("rope_rows: rotated entries fall outside the row")
-    _check(library().tlb_rope_rows(_ptr(x), x.stride(0), head_stride, first, heads, dims, int(interleaved), float(base), _ptr(tok_pos), x.shape[0],
-                                   _code(x.dtype), _stream(x)))
+    _check(library().tlb_rope_rows(_ptr(x), x.stride(0), head_stride, first, heads, dims, int(interleaved), float(base), float(factor), _ptr(tok_pos),
+                                   x.shape[0], _code(x.dtype), _stream(x)))
     return x
+
+
+def rope_table(tok_pos: torch.Tensor, *, dims: int, base: float, factor: float = 1.0):
+    """-> (cos, sin) fp32 ``[rows, dims // 2]`` of ``tok_pos * base^(-2i/dims) / factor``, for kernels that rotate in fp32."""
+    _gpu("rope_table", tok_pos)
+    if tok_pos.dtype != torch.int32 or tok_pos.dim() != 1 or not tok_pos.is_contiguous() or dims <= 0 or dims % 2:
+        raise RuntimeError("rope_table: tok_pos must be contiguous int32 [rows] and dims even")
+    rows = tok_pos.numel()
+    cs = torch.empty((rows, dims // 2), dtype=torch.float32, device=tok_pos.device)
+    sn = torch.empty_like(cs)
+    _check(library().tlb_rope_table(_ptr(tok_pos), rows, int(dims), float(base), float(factor), _ptr(cs), _ptr(sn), _stream(tok_pos)))
+    return cs, sn
 
 
 def latent_append(down, norm_weight, eps, *, rank, rot_dims, interleaved, base, tok_pos, tok_seq, block_table, slab):
@@ -302,24 +323,28 @@ def gated_act(gate_up: torch.Tensor, act: int) -> torch.Tensor:
     return out
 
 
-def moe_route(h, router_w, router_b, top: int, scoring: int = SCORE_SOFTMAX):
-    """-> (expert ids int32 [T, top], weights fp32 [T, top]): softmax over the chosen logits, or each one's sigmoid."""
-    _gpu("moe_route", h, router_w, router_b)
-    _contig("moe_route", h, router_w, router_b)
+def moe_route(h, router_w, router_b, top: int, scoring: int = SCORE_SOFTMAX, choice_bias=None, weight_scale: float = 1.0):
+    """-> (expert ids int32 [T, top], weights fp32 [T, top]): softmax over the chosen logits, each one's sigmoid, or
+    (``SCORE_SOFTMAX_ALL``) a softmax over all outputs, chosen by score + ``choice_bias``, the chosen scores renormalised
+    and times ``weight_scale``."""
+    _gpu("moe_route", h, router_w, router_b, choice_bias)
+    _contig("moe_route", h, router_w, router_b, choice_bias)
+    if choice_bias is not None and (choice_bias.dtype != h.dtype or choice_bias.numel() != router_w.shape[0]):
+        raise RuntimeError("moe_route: choice_bias must be [experts] of the activations' dtype")
     T, D = h.shape
     E = router_w.shape[0]
     idx = torch.empty((T, top), dtype=torch.int32, device=h.device)
     gate = torch.empty((T, top), dtype=torch.float32, device=h.device)
-    _check(library().tlb_moe_route(_ptr(h), _ptr(router_w), _ptr(router_b), T, D, E, top, int(scoring), _ptr(idx), _ptr(gate), _code(h.dtype),
-                                   _stream(h)))
+    _check(library().tlb_moe_route(_ptr(h), _ptr(router_w), _ptr(router_b), T, D, E, top, int(scoring), _ptr(choice_bias), float(weight_scale), _ptr(idx),
+                                   _ptr(gate), _code(h.dtype), _stream(h)))
     return idx, gate
 
 
-def moe_experts(h, idx, gate, w_gate, w_up, w_down, act: int, shared=None, scale_input: bool = False) -> torch.Tensor:
+def moe_experts(h, idx, gate, w_gate, w_up, w_down, act: int, shared=None, scale_input: bool = False, identity: bool = False) -> torch.Tensor:
     """Sum of the chosen experts' feed-forwards (+ ``shared [T, D]``) -> fp32 ``[T, D]``.  ``w_up [E, ff, D]``,
     ``w_down [E, D, ff]``; with ``w_gate [E, ff, D]`` an expert is ``down(act(gate x) * (up x))``, without it
     ``down(act(up x))``.  The router's weight multiplies the expert's output, or, ``scale_input``, its input ``x``
-    (rounded to the compute dtype)."""
+    (rounded to the compute dtype).  ``identity``: ids from ``E`` up name identity experts, whose output is the token itself."""
     _gpu("moe_experts", h, idx, gate, w_gate, w_up, w_down, shared)
     _contig("moe_experts", h, idx, gate, w_gate, w_up, w_down, shared)
     lib = library()
@@ -350,21 +375,23 @@ def moe_experts(h, idx, gate, w_gate, w_up, w_down, act: int, shared=None, scale
         _check(lib.tlb_moe_up(_ptr(rows_in), _ptr(w_up), _ptr(sorted_pair), _ptr(tile_expert), _ptr(counters), T, top, E, rows, D, ff, act, per_pair,
                               _ptr(inter), code, st))
     _check(lib.tlb_moe_down(_ptr(inter), _ptr(w_down), _ptr(sorted_pair), _ptr(tile_expert), _ptr(counters), T, top, E, rows, D, ff, _ptr(pair_out), code, st))
-    _check(lib.tlb_moe_combine(_ptr(pair_out), None if scale_input else _ptr(gate), _ptr(shared), _ptr(y), T, top, D, code, st))
+    _check(lib.tlb_moe_combine(_ptr(pair_out), None if scale_input else _ptr(gate), _ptr(shared), _ptr(idx) if identity else None, E,
+                               _ptr(h) if identity else None, _ptr(y), T, top, D, code, st))
     return y
 
 
 def add_norm(residual: torch.Tensor, a: torch.Tensor, b: torch.Tensor | None, weight: torch.Tensor | None, eps: float):
-    """``residual += a (+ b)`` (all fp32 ``[rows, dim]``, in place); with ``weight`` also returns the RMS norm of the new
-    residual times ``weight``, rounded to the weight's dtype."""
+    """``residual += a (+ b)`` (all fp32 ``[rows, dim]``, in place; ``a`` may be one row ``[dim]`` for all); with ``weight``
+    also returns the RMS norm of the new residual times ``weight``, rounded to the weight's dtype."""
     _gpu("add_norm", residual, a, b, weight)
     _contig("add_norm", residual, a, b, weight)
     rows, dim = residual.shape
-    if residual.dtype != torch.float32 or a.dtype != torch.float32 or a.shape != residual.shape or (b is not None and (b.dtype != torch.float32 or b.shape != residual.shape)):
+    a_row = a.dim() == 1
+    if residual.dtype != torch.float32 or a.dtype != torch.float32 or a.shape != (residual.shape[1:] if a_row else residual.shape) or (b is not None and (b.dtype != torch.float32 or b.shape != residual.shape)):
         raise RuntimeError("add_norm: residual and addends must be float32 of one shape")
     h = None if weight is None else torch.empty((rows, dim), dtype=weight.dtype, device=residual.device)
     code = _code(weight.dtype) if weight is not None else 0
-    _check(library().tlb_add_norm(_ptr(residual), _ptr(a), _ptr(b), _ptr(weight), float(eps), _ptr(h), rows, dim, code, _stream(residual)))
+    _check(library().tlb_add_norm(_ptr(residual), _ptr(a), int(a_row), _ptr(b), _ptr(weight), float(eps), _ptr(h), rows, dim, code, _stream(residual)))
     return h
 
 
@@ -465,16 +492,30 @@ def paged_attention(q, slab, block_table, tiles, tok_pos, *, kv_heads: int, dv: 
     return out
 
 
-def decay_scan(q, k, v, z, z_bias, *, tau: float, q_scale: float, seq_info, state, out=None, max_tokens: int | None = None):
+def decay_scan(q, k, v, z, z_bias, *, tau: float = 1.0, q_scale: float, seq_info, state, out=None, max_tokens: int | None = None, head_decay=None,
+               rope=None, rope_dims: int = 0, rope_interleaved: bool = False):
     """Linear attention with per-channel decay ``sigmoid(z + z_bias)^(1/tau)``: ``q, k [T, H, dk]``, ``v [T, H, dv]`` views,
     ``z [T, H * dk]`` fp32, ``seq_info [S, 4]`` int32 (first token, count, start position, slot), ``state [slots, H, dk, dv]``
     fp32 (a view whose slots may be further apart) -> fp32 ``[T, H, dv]``.  ``max_tokens``: the largest count in
-    ``seq_info`` (default: all tokens); portions longer than a segment run as parallel segments over a workspace."""
-    _gpu("decay_scan", q, k, v, z, z_bias, seq_info, state, out)
+    ``seq_info`` (default: all tokens); portions longer than a segment run as parallel segments over a workspace.
+    ``head_decay`` (fp32 ``[H]``) replaces the logits by one fixed decay per head (``z`` None).  ``rope`` = (cos, sin) tables
+    of ``rope_table`` for this step's tokens: the first ``rope_dims`` entries of every head of q and k are rotated in fp32
+    on their way in."""
+    _gpu("decay_scan", q, k, v, z, z_bias, seq_info, state, out, head_decay)
     T, H, dk = q.shape
     dv = v.shape[2]
-    if k.shape != (T, H, dk) or v.shape[:2] != (T, H) or z.shape != (T, H * dk) or z.dtype != torch.float32 or z.stride(1) != 1:
+    if k.shape != (T, H, dk) or v.shape[:2] != (T, H):
         raise RuntimeError("decay_scan: shapes do not match")
+    if head_decay is not None:
+        if z is not None or head_decay.dtype != torch.float32 or head_decay.shape != (H,) or not head_decay.is_contiguous():
+            raise RuntimeError("decay_scan: head_decay must be float32 [H] and replaces z")
+    elif z is None or z.shape != (T, H * dk) or z.dtype != torch.float32 or z.stride(1) != 1:
+        raise RuntimeError("decay_scan: shapes do not match")
+    cs = sn = None
+    if rope_dims:
+        cs, sn = rope
+        if cs.shape != (T, rope_dims // 2) or sn.shape != cs.shape or cs.dtype != torch.float32 or not cs.is_contiguous() or not sn.is_contiguous() or rope_dims > dk:
+            raise RuntimeError("decay_scan: rotation tables must be float32 [T, rope_dims / 2]")
     if q.stride(2) != 1 or k.stride(2) != 1 or v.stride(2) != 1 or not (q.dtype == k.dtype == v.dtype):
         raise RuntimeError("decay_scan: unit inner strides and one dtype wanted")
     if state.dtype != torch.float32 or state.shape[1:] != (H, dk, dv) or not state[0].is_contiguous():
@@ -488,23 +529,106 @@ def decay_scan(q, k, v, z, z_bias, *, tau: float, q_scale: float, seq_info, stat
     nbytes = int(lib.tlb_decay_scan_workspace(seq_info.shape[0], longest, H, dk, dv))
     ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device) if nbytes else None
     _check(lib.tlb_decay_scan(_ptr(q), q.stride(0), q.stride(1), _ptr(k), k.stride(0), k.stride(1), _ptr(v), v.stride(0), v.stride(1), _ptr(z),
-                              z.stride(0), _ptr(z_bias), float(tau), float(q_scale), H, dk, dv, _ptr(seq_info), seq_info.shape[0], longest, _ptr(state),
+                              z.stride(0) if z is not None else 0, _ptr(z_bias), float(tau), _ptr(head_decay), _ptr(cs), _ptr(sn), int(rope_dims),
+                              int(bool(rope_interleaved)), float(q_scale), H, dk, dv, _ptr(seq_info), seq_info.shape[0], longest, _ptr(state),
                               state.stride(0), state.shape[0], _ptr(out), _ptr(ws), nbytes, _code(q.dtype), _stream(q)))
     return out
 
 
 def head_norm_gate(o, weight, eps: float, gate=None, act: int = 1):
-    """``o [T, H, dv]`` fp32 -> ``[T, H * dv]`` in the weight's dtype: per-head RMS norm times ``weight [dv]`` times
-    ``silu(gate)`` (``act`` 1) or ``gate`` (0); ``gate [T, H * dv]`` a view with unit inner stride."""
+    """``o [T, H, dv]`` fp32 -> ``[T, H * dv]`` in the weight's (without one: the gate's) dtype: per-head RMS norm times
+    ``weight [dv]`` (None = no weight) times ``silu(gate)`` (``act`` 1), ``sigmoid(gate)`` (2) or ``gate`` (0);
+    ``gate [T, H * dv]`` a view with unit inner stride."""
     _gpu("head_norm_gate", o, weight, gate)
     _contig("head_norm_gate", o, weight)
     T, H, dv = o.shape
-    if o.dtype != torch.float32 or weight.shape != (dv,) or (gate is not None and (gate.shape != (T, H * dv) or gate.stride(1) != 1 or gate.dtype != weight.dtype)):
+    if weight is None and gate is None:
+        raise RuntimeError("head_norm_gate: a weight or a gate must name the output dtype")
+    dtype = weight.dtype if weight is not None else gate.dtype
+    if o.dtype != torch.float32 or (weight is not None and weight.shape != (dv,)) or (gate is not None and (gate.shape != (T, H * dv) or gate.stride(1) != 1 or gate.dtype != dtype)):
         raise RuntimeError("head_norm_gate: shapes do not match")
-    out = torch.empty((T, H * dv), dtype=weight.dtype, device=o.device)
+    out = torch.empty((T, H * dv), dtype=dtype, device=o.device)
     _check(library().tlb_head_norm_gate(_ptr(o), _ptr(weight), float(eps), _ptr(gate), gate.stride(0) if gate is not None else 0, int(act), _ptr(out),
-                                        T, H, dv, _code(weight.dtype), _stream(o)))
+                                        T, H, dv, _code(dtype), _stream(o)))
     return out
+
+
+def delta_scan(q, k, v, beta, a, a_log, dt_bias, *, per_channel: bool, q_scale: float, unit_eps: float = 1e-6, seq_info, state, out=None):
+    """Gated delta rule: ``q, k [T, G, dk]``, ``v [T, H, dv]``, ``beta [T, H]`` (logits) views in one dtype; ``a`` the decay
+    input, ``[T, H]`` (one decay per head, ``dt_bias [H]``) or ``[T, H * dk]`` (one per key channel, ``dt_bias [H * dk]``),
+    fp32 or that dtype; ``a_log [H]``; ``state [slots, H, dk, dv]`` fp32 -> fp32 ``[T, H, dv]``."""
+    _gpu("delta_scan", q, k, v, beta, a, a_log, dt_bias, seq_info, state, out)
+    _contig("delta_scan", a_log, dt_bias, seq_info)
+    T, G, dk = q.shape
+    H, dv = v.shape[1], v.shape[2]
+    if k.shape != (T, G, dk) or v.shape[0] != T or beta.shape != (T, H) or H % G or a_log.shape != (H,):
+        raise RuntimeError("delta_scan: shapes do not match")
+    if a.shape != ((T, H * dk) if per_channel else (T, H)) or dt_bias.numel() != (H * dk if per_channel else H):
+        raise RuntimeError("delta_scan: the decay input must be [T, H] or [T, H * dk] with a bias of that width")
+    if q.stride(2) != 1 or k.stride(2) != 1 or v.stride(2) != 1 or beta.stride(1) != 1 or a.stride(1) != 1 or not (q.dtype == k.dtype == v.dtype == beta.dtype == a_log.dtype == dt_bias.dtype):
+        raise RuntimeError("delta_scan: unit inner strides and one dtype wanted")
+    if a.dtype not in (torch.float32, q.dtype):
+        raise RuntimeError("delta_scan: the decay input must be float32 or the activations' dtype")
+    if state.dtype != torch.float32 or state.shape[1:] != (H, dk, dv) or not state[0].is_contiguous():
+        raise RuntimeError("delta_scan: state must be float32 [slots, H, dk, dv]")
+    if seq_info.dtype != torch.int32 or seq_info.dim() != 2 or seq_info.shape[1] != 4:
+        raise RuntimeError("delta_scan: seq_info must be int32 [S, 4]")
+    if out is None:
+        out = torch.empty((T, H, dv), dtype=torch.float32, device=q.device)
+    _check(library().tlb_delta_scan(_ptr(q), q.stride(0), q.stride(1), _ptr(k), k.stride(0), k.stride(1), _ptr(v), v.stride(0), v.stride(1), _ptr(beta),
+                                    beta.stride(0), _ptr(a), int(a.dtype == torch.float32), a.stride(0), int(per_channel), _ptr(a_log), _ptr(dt_bias),
+                                    float(q_scale), float(unit_eps), H, G, dk, dv, _ptr(seq_info), seq_info.shape[0], _ptr(state), state.stride(0),
+                                    state.shape[0], _ptr(out), _code(q.dtype), _stream(q)))
+    return out
+
+
+def short_conv(x, taps, *, seq_info, state, max_tokens: int, act: int = 1):
+    """Causal convolution per channel along every sequence, then silu (``act`` 1): ``x [T, C]`` (a view with unit inner
+    stride), ``taps [C, K]``, ``state [slots, C, K - 1]`` fp32 (a view whose slots may be further apart): the inputs before
+    the step's first token, replaced by the step's last ones -> ``[T, C]`` contiguous in x's dtype."""
+    _gpu("short_conv", x, taps, seq_info, state)
+    _contig("short_conv", taps, seq_info)
+    T, C = x.shape
+    K = taps.shape[1]
+    if taps.shape[0] != C or taps.dtype != x.dtype or x.stride(1) != 1:
+        raise RuntimeError("short_conv: taps must be [C, K] of x's dtype")
+    if K > 1 and (state is None or state.dtype != torch.float32 or state.shape[1:] != (C, K - 1) or not state[0].is_contiguous()):
+        raise RuntimeError("short_conv: state must be float32 [slots, C, K - 1]")
+    y = torch.empty((T, C), dtype=x.dtype, device=x.device)
+    _check(library().tlb_short_conv(_ptr(x), x.stride(0), _ptr(taps), C, K, int(act), _ptr(seq_info), seq_info.shape[0], max(1, int(max_tokens)),
+                                    _ptr(state) if K > 1 else None, state.stride(0) if K > 1 else 0, state.shape[0] if K > 1 else 0, _ptr(y),
+                                    _code(x.dtype), _stream(x)))
+    return y
+
+
+def act_rows(x: torch.Tensor, act: int) -> torch.Tensor:
+    """``act(x)`` elementwise (``ACT_SILU``, ``ACT_GELU_TANH``, ``ACT_RELU_SQUARED``)."""
+    _gpu("act_rows", x)
+    _contig("act_rows", x)
+    out = torch.empty_like(x)
+    _check(library().tlb_act_rows(_ptr(x), _ptr(out), x.shape[0], x.shape[1], int(act), _code(x.dtype), _stream(x)))
+    return out
+
+
+def softcap_rows(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """``cap * tanh(x / cap)`` of fp32 ``[rows, width]``, in place."""
+    _gpu("softcap_rows", x)
+    _contig("softcap_rows", x)
+    if x.dtype != torch.float32 or x.dim() != 2:
+        raise RuntimeError("softcap_rows: expected float32 [rows, width]")
+    _check(library().tlb_softcap_rows(_ptr(x), x.shape[0], x.shape[1], float(cap), _stream(x)))
+    return x
+
+
+def cast_rows(src: torch.Tensor, dst: torch.Tensor) -> torch.Tensor:
+    """``dst[:, :] = src`` rounded to dst's dtype; ``src`` fp32 ``[rows, dim]`` contiguous, ``dst`` a column block (unit
+    inner stride) of a wider matrix."""
+    _gpu("cast_rows", src, dst)
+    _contig("cast_rows", src)
+    if src.dtype != torch.float32 or src.shape != dst.shape or dst.stride(1) != 1:
+        raise RuntimeError("cast_rows: float32 [rows, dim] into a view of the same shape")
+    _check(library().tlb_cast_rows(_ptr(src), _ptr(dst), dst.stride(0), src.shape[0], src.shape[1], _code(dst.dtype), _stream(src)))
+    return dst
 
 
 def argmax_rows(logits: torch.Tensor) -> torch.Tensor:

@@ -1,4 +1,5 @@
-"""Linear attention with a per-channel decay: a recurrent mixer whose state lives in fp32 slots.
+"""Linear attention with a decay: recurrent mixers whose state lives in fp32 slots.  ``DecayedLinearAttention`` has one
+input-dependent decay per key channel, ``RetainedLinearAttention`` (at the end of the file) one fixed decay per head.
 
 Per head a matrix ``S [dim, vdim]`` is carried along the sequence,
 
@@ -41,3 +42,40 @@ class DecayedLinearAttention:
         o = blocks.decay_scan(q.unflatten(1, (H, self.dim)), k.unflatten(1, (H, self.dim)), v.unflatten(1, (H, self.vdim)), z, self.a2_bias,
                               tau=self.tau, q_scale=self.dim ** -0.5, seq_info=plan.seq_info, state=state, max_tokens=plan.max_tokens)
         return linear_wide(blocks.head_norm_gate(o, self.norm_weight, self.eps, gate, act=1), self.w_o)
+
+
+class RetainedLinearAttention:
+    """Retention: linear attention with ONE fixed decay per head and no denominator,
+
+        S_t = decay_h S_(t-1) + k_t v_t^T        o_t = S_t^T q_t        (dim^-1/2 folded into q)
+
+    with q and k optionally rotated by the token's position first (``rot`` = ``{"dims", "base", "factor"}``, pairs
+    ``(i, i + dims/2)``; in fp32, inside the scan, from the step's tabulated angles).  Each head's output is divided by its
+    root mean square (no weight), multiplied by ``silu(gate)`` and projected.  The scan is ``blocks.decay_scan`` with a
+    constant decay, so long portions run as parallel segments like those of ``DecayedLinearAttention``."""
+
+    def __init__(self, *, heads: int, dim: int, vdim: int, decay, w_o, eps: float = 1e-6, rot: dict | None = None):
+        if len(decay) != heads or tuple(w_o.shape)[1] != heads * vdim:
+            raise ValueError("retention: one decay per head and an output projection of heads x vdim wanted")
+        self.heads, self.dim, self.vdim, self.eps = int(heads), int(dim), int(vdim), float(eps)
+        self.decay = torch.tensor([float(d) for d in decay], dtype=torch.float32, device=w_o.device)
+        self.w_o = w_o.contiguous()
+        self.rot = None
+        if rot and int(rot.get("dims", 0)) > 0:
+            self.rot = {"dims": int(rot["dims"]), "base": float(rot["base"]), "factor": float(rot.get("factor", 1.0))}
+            if self.rot["dims"] % 2 or self.rot["dims"] > self.dim:
+                raise ValueError(f"retention: cannot rotate {self.rot['dims']} of {self.dim} entries")
+
+    @property
+    def state_shape(self) -> tuple:
+        return (self.heads, self.dim, self.vdim)
+
+    def __call__(self, q, k, v, gate, plan, state: torch.Tensor) -> torch.Tensor:
+        from extensions_b200.tiny_llm_ext_b200 import blocks
+
+        H, r = self.heads, self.rot
+        tables = plan.rope_tables(r["dims"], r["base"], r["factor"]) if r else None
+        o = blocks.decay_scan(q.unflatten(1, (H, self.dim)), k.unflatten(1, (H, self.dim)), v.unflatten(1, (H, self.vdim)), None, None,
+                              q_scale=self.dim ** -0.5, seq_info=plan.seq_info, state=state, max_tokens=plan.max_tokens, head_decay=self.decay,
+                              rope=tables, rope_dims=r["dims"] if r else 0, rope_interleaved=False)
+        return linear_wide(blocks.head_norm_gate(o, None, self.eps, gate, act=1), self.w_o)

@@ -15,7 +15,19 @@ import torch
 from .basics import linear, linear_wide
 
 ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "relu_squared": 2}
-SCORINGS = {"softmax": 0, "sigmoid": 1}
+SCORINGS = {"softmax": 0, "sigmoid": 1, "softmax_all": 2}
+
+
+class DenseMLP:
+    """The ungated feed-forward ``down(act(up x))``; the down projection hands its fp32 accumulator on."""
+
+    def __init__(self, w_up: torch.Tensor, w_down: torch.Tensor, act: str):
+        self.w_up, self.w_down, self.act = w_up.contiguous(), w_down.contiguous(), ACTIVATIONS[act]
+
+    def __call__(self, h: torch.Tensor) -> torch.Tensor:
+        from extensions_b200.tiny_llm_ext_b200 import blocks
+
+        return linear_wide(blocks.act_rows(linear(h, self.w_up), self.act), self.w_down)
 
 
 class GatedMLP:
@@ -32,9 +44,15 @@ class GatedMLP:
 
 
 class TopKRouter:
-    def __init__(self, weight: torch.Tensor, bias: torch.Tensor | None, top: int, scoring: str = "softmax"):
+    def __init__(self, weight: torch.Tensor, bias: torch.Tensor | None, top: int, scoring: str = "softmax", choice_bias: torch.Tensor | None = None,
+                 weight_scale: float = 1.0):
+        """``scoring="softmax_all"``: scores are a softmax over ALL router outputs, the ``top`` are chosen by score +
+        ``choice_bias`` (which the weights do not see), the chosen scores are renormalised and times ``weight_scale``."""
         self.weight, self.bias, self.top = weight.contiguous(), None if bias is None else bias.contiguous(), int(top)
         self.scoring = SCORINGS[scoring]
+        self.choice_bias, self.weight_scale = None if choice_bias is None else choice_bias.contiguous(), float(weight_scale)
+        if (choice_bias is not None or self.weight_scale != 1.0) and scoring != "softmax_all":
+            raise ValueError("router: a choice bias and a weight scale go with scoring='softmax_all'")
         if not 0 < self.top <= weight.shape[0]:
             raise ValueError(f"router: top={top} of {weight.shape[0]} experts")
 
@@ -42,15 +60,21 @@ class TopKRouter:
         """-> (expert ids int32 [T, top], weights fp32 [T, top])."""
         from extensions_b200.tiny_llm_ext_b200 import blocks
 
-        return blocks.moe_route(h, self.weight, self.bias, self.top, self.scoring)
+        return blocks.moe_route(h, self.weight, self.bias, self.top, self.scoring, self.choice_bias, self.weight_scale)
 
 
 class MixtureOfExperts:
     def __init__(self, router: TopKRouter, w_gate: torch.Tensor | None, w_up: torch.Tensor, w_down: torch.Tensor, act: str,
-                 shared: GatedMLP | None = None, weight_on: str = "output"):
-        """``w_gate, w_up [E, ff, D]``, ``w_down [E, D, ff]`` (the experts stacked); ``w_gate`` None = experts without a gate."""
+                 shared: GatedMLP | None = None, weight_on: str = "output", identity: int = 0):
+        """``w_gate, w_up [E, ff, D]``, ``w_down [E, D, ff]`` (the experts stacked); ``w_gate`` None = experts without a gate.
+        ``identity``: the router's last ``identity`` outputs are experts without weights whose output is their input."""
         if weight_on not in ("output", "input"):
             raise ValueError(f"weight_on={weight_on!r}")
+        self.identity = int(identity)
+        if self.identity < 0 or router.weight.shape[0] != w_up.shape[0] + self.identity:
+            raise ValueError(f"router outputs ({router.weight.shape[0]}) != experts ({w_up.shape[0]}) + identity experts ({identity})")
+        if self.identity and weight_on == "input":
+            raise ValueError("identity experts take the router's weight on their output")
         self.router, self.shared, self.scale_input = router, shared, weight_on == "input"
         self.w_gate, self.w_up, self.w_down = None if w_gate is None else w_gate.contiguous(), w_up.contiguous(), w_down.contiguous()
         self.act = ACTIVATIONS[act]
@@ -61,4 +85,4 @@ class MixtureOfExperts:
 
         idx, gate = self.router(h)
         shared = None if self.shared is None else self.shared(h)
-        return blocks.moe_experts(h, idx, gate, self.w_gate, self.w_up, self.w_down, self.act, shared, scale_input=self.scale_input)
+        return blocks.moe_experts(h, idx, gate, self.w_gate, self.w_up, self.w_down, self.act, shared, scale_input=self.scale_input, identity=self.identity > 0)

@@ -19,6 +19,7 @@ MODEL_SHORTCUTS = {
 ARCHITECTURES = {
     "Voluzen": ("tiny_llm_b200.voluzen", "VoluzenModel"),
     "Bapovik": ("tiny_llm_b200.bapovik", "BapovikModel"),
+    "Senurax": ("tiny_llm_b200.senurax", "SenuraxModel"),
 }
 
 

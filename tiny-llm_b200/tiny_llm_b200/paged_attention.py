@@ -2,8 +2,10 @@
 parameters: what a position sees (``mask`` = ``"causal"``, ``"window"``: itself and the ``mask_size - 1`` positions
 before it, ``"chunk"``: the earlier positions of its own block of ``mask_size`` positions counted from 0), a tanh
 ``softcap`` on the scaled scores, a ``sink`` (one more term ``exp(0)`` in the softmax's denominator), per-head RMS
-norms of queries and keys (plain weights of size ``dim``, shared by the heads) and a sigmoid output gate per head.
-The scores carry no positional term (nothing is rotated).
+norms of queries and keys (plain weights of size ``dim``, shared by the heads) and a sigmoid output gate per head
+(``gate`` None = no gate).  With ``rot`` = ``{"dims", "base", "factor", "interleaved"}`` the first ``dims`` entries of every
+query and key head are rotated by the token's position (pairs ``(2i, 2i+1)`` or ``(i, i + dims/2)``, every frequency
+divided by ``factor``) before the keys are stored; without it the scores carry no positional term.
 
 The layer's input projections are made by the caller in one product (``FusedProjection``); the module takes the views
 ``q [T, H * dim]``, ``k [T, G * dim]``, ``v [T, G * vdim]`` and ``gate [T, H]`` (logits), stores keys and values in the
@@ -46,7 +48,7 @@ class FusedProjection:
 
 class PagedGroupedAttention:
     def __init__(self, *, heads: int, kv_heads: int, dim: int, vdim: int, scale: float, mask: str, mask_size: int, w_o, softcap: float | None = None,
-                 sink: bool = False, q_norm=None, k_norm=None, eps: float = 1e-6, caches: bool = True, page_size: int = 64):
+                 sink: bool = False, q_norm=None, k_norm=None, eps: float = 1e-6, caches: bool = True, page_size: int = 64, rot: dict | None = None):
         if heads % kv_heads:
             raise ValueError(f"{heads} query heads do not divide into {kv_heads} key/value heads")
         if mask not in MASKS or (mask != "causal" and int(mask_size) <= 0):
@@ -59,6 +61,13 @@ class PagedGroupedAttention:
         self.q_norm = None if q_norm is None else q_norm.contiguous()
         self.k_norm = None if k_norm is None else k_norm.contiguous()
         self.w_o = w_o.contiguous()
+        self.rot = None
+        if rot and int(rot.get("dims", 0)) > 0:
+            if q_norm is not None or k_norm is not None:
+                raise ValueError("attention: rotation together with query / key norms is not built")
+            self.rot = {"dims": int(rot["dims"]), "base": float(rot["base"]), "factor": float(rot.get("factor", 1.0)), "interleaved": bool(rot.get("interleaved", False))}
+            if self.rot["dims"] % 2 or self.rot["dims"] > self.dim:
+                raise ValueError(f"attention: cannot rotate {self.rot['dims']} of {self.dim} entries")
         from extensions_b200.tiny_llm_ext_b200 import blocks
 
         # the kernel (tensor cores for a bf16 cache of fitting sizes, else the general one) and its work-list granularity
@@ -73,6 +82,11 @@ class PagedGroupedAttention:
 
         T, H, G = q.shape[0], self.heads, self.kv_heads
         q3 = q.unflatten(1, (H, self.dim))
+        if self.rot is not None:
+            r = self.rot
+            blocks.rope_rows(q, plan.tok_pos, heads=H, head_stride=self.dim, first=0, dims=r["dims"], base=r["base"], interleaved=r["interleaved"], factor=r["factor"])
+            if self.caches:
+                blocks.rope_rows(k, plan.tok_pos, heads=G, head_stride=self.dim, first=0, dims=r["dims"], base=r["base"], interleaved=r["interleaved"], factor=r["factor"])
         if self.caches:
             blocks.kv_prepare(q3, k.unflatten(1, (G, self.dim)), v.unflatten(1, (G, self.vdim)), q_norm=self.q_norm, k_norm=self.k_norm, eps=self.eps,
                               tok_pos=plan.tok_pos, tok_seq=plan.tok_seq, block_table=plan.block_table, slab=slab)

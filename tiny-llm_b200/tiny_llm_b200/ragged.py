@@ -128,6 +128,16 @@ class RaggedPlan:
             if hasattr(o, "ran_offset"):
                 o.ran_offset = o.offset
 
+    def rope_tables(self, dims: int, base: float, factor: float = 1.0):
+        """(cos, sin) fp32 ``[T, dims // 2]`` of this step's token positions, made once per step and rotation."""
+        from extensions_b200.tiny_llm_ext_b200 import blocks
+
+        key = (int(dims), float(base), float(factor))
+        tables = self.__dict__.setdefault("_rope_tables", {})
+        if key not in tables:
+            tables[key] = blocks.rope_table(self.tok_pos, dims=key[0], base=key[1], factor=key[2])
+        return tables[key]
+
     def tiles_for(self, size: int) -> torch.Tensor:
         """The work list cut into runs of at most ``size`` tokens (one of the sizes the plan was built for)."""
         return self._tiles[size]

@@ -345,3 +345,113 @@ def synthetic_bapovik(config: dict, seed: int = 0, dtype=torch.bfloat16) -> dict
 
 
 save_bapovik = save_voluzen  # the same directory layout: config.json + model.safetensors
+
+
+# ---- Senurax (retention / gated delta rule / softmax attention beside a delta rule, looped layers; senurax.py) -------
+def senurax_config(*, width=96, vocab=200, pattern="RdCmCdPm", loop=(1, 3, 2), heads=4, kv_heads=2, dim=16, vdim=24, rot_dims=8, rot_base=10000.0,
+                   rot_factor=2.0, scale=None, rec_heads=4, rec_key_heads=2, rec_dim=16, rec_vdim=32, taps=4, ret_heads=2, ret_dim=16, ret_vdim=32,
+                   ret_rot_dims=16, decay=None, ff=160, experts=6, identity=2, top=2, expert_ff=40, router_scale=1.5, softcap=20.0, eps=1e-5) -> dict:
+    """A config.json for a stack spelled by ``pattern``, two letters a layer: the mixer (``R`` retention, ``C`` gated delta
+    rule with per-channel decay, ``P`` softmax attention beside a gated delta rule) and the feed-forward (``d`` dense,
+    ``m`` experts, ``n`` none).  ``loop`` = (start, stop, times) or None."""
+    if len(pattern) % 2:
+        raise ValueError("the pattern is pairs of letters: mixer, feed-forward")
+    layers = []
+    for mixer_letter, ff_letter in zip(pattern[0::2], pattern[1::2]):
+        if ff_letter == "d":
+            mlp = {"kind": "dense", "ff": ff}
+        elif ff_letter == "m":
+            mlp = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "identity": identity, "top": top, "scale": router_scale}}
+        elif ff_letter == "n":
+            mlp = None
+        else:
+            raise ValueError(f"unknown feed-forward letter {ff_letter!r}")
+        delta = {"conv": taps, "dim": rec_dim, "heads": rec_heads, "kv_heads": rec_key_heads, "vdim": rec_vdim}
+        if mixer_letter == "R":
+            d = list(decay) if decay is not None else [1.0 - 2.0 ** (-3 - 1.5 * h) for h in range(ret_heads)]
+            mixer = {"heads": ret_heads, "dim": ret_dim, "vdim": ret_vdim, "decay": d}
+            if ret_rot_dims:
+                mixer["rot"] = {"base": rot_base, "dims": ret_rot_dims}
+            layers.append({"type": "retention", "mixer": mixer, "mlp": mlp})
+        elif mixer_letter == "C":
+            layers.append({"type": "channel_delta", "mixer": delta, "mlp": mlp})
+        elif mixer_letter == "P":
+            left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": float(scale if scale is not None else dim ** -0.5)}
+            if rot_dims:
+                left["rot"] = {"base": rot_base, "dims": rot_dims}
+                if rot_factor and rot_factor != 1.0:
+                    left["rot"]["scaling"] = {"factor": rot_factor}
+            layers.append({"type": "parallel", "mixer": {"left": left, "right": delta}, "mlp": mlp})
+        else:
+            raise ValueError(f"unknown mixer letter {mixer_letter!r}")
+    config = {"architecture": "Senurax", "vocab": vocab, "width": width, "norm": {"eps": eps}, "layers": layers}
+    if softcap:
+        config["logit_softcap"] = softcap
+    if loop:
+        config["loop"] = {"start": loop[0], "stop": loop[1], "times": loop[2]}
+    return config
+
+
+def synthetic_senurax(config: dict, seed: int = 0, dtype=torch.bfloat16) -> dict:
+    """Random tensors for ``config`` under the checkpoint's names (CPU, seeded)."""
+    gen = torch.Generator().manual_seed(seed)
+    D = config["width"]
+
+    def mat(out_dim, in_dim, gain=1.0):
+        return (torch.randn(out_dim, in_dim, generator=gen) * (gain / in_dim**0.5)).to(dtype)
+
+    def vec(n, centre, spread):
+        return (centre + spread * torch.randn(n, generator=gen)).to(dtype)
+
+    tensors = {"embed": torch.randn(config["vocab"], D, generator=gen).to(dtype), "final.norm": vec(D, 1.0, 0.1), "head": mat(config["vocab"], D)}
+    if config.get("loop"):
+        times = config["loop"]["times"]
+        tensors["loop.in"] = torch.cat([mat(D, D), mat(D, D, 0.5)], dim=1).contiguous()
+        tensors["loop.step"] = (0.3 * torch.randn(times, D, generator=gen)).to(dtype)
+
+    def delta(p, m, channel):
+        H, G, dk, dv, K = m["heads"], m.get("kv_heads", m["heads"]), m["dim"], m["vdim"], m["conv"]
+        for name, rows in (("q", G * dk), ("k", G * dk), ("v", H * dv)):
+            tensors[p + name] = mat(rows, D, 2.0)
+            tensors[p + name + ".conv"] = (torch.randn(rows, K, generator=gen) * 0.5 + torch.eye(K)[K - 1]).to(dtype)
+        tensors[p + "b"], tensors[p + "A_log"], tensors[p + "norm"], tensors[p + "o"] = mat(H, D, 2.0), vec(H, -1.0, 1.0), vec(dv, 1.0, 0.2), mat(D, H * dv)
+        if channel:
+            low = max(4, D // 12)
+            tensors[p + "a1"], tensors[p + "a2"], tensors[p + "dt_bias"] = mat(low, D), mat(H * dk, low, 2.0), vec(H * dk, -1.0, 1.0)
+            tensors[p + "g1"], tensors[p + "g2"] = mat(low, D), mat(H * dv, low, 2.0)
+        else:
+            tensors[p + "a"], tensors[p + "dt_bias"], tensors[p + "g"] = mat(H, D, 2.0), vec(H, -1.0, 1.0), mat(H * dv, D)
+
+    for i, layer in enumerate(config["layers"]):
+        m, p = layer["mixer"], f"l{i}."
+        tensors[p + "norm1"] = vec(D, 1.0, 0.1)
+        if layer["type"] == "retention":
+            H, dk, dv = m["heads"], m["dim"], m["vdim"]
+            tensors[p + "mix.q"], tensors[p + "mix.k"], tensors[p + "mix.v"] = mat(H * dk, D, 2.0), mat(H * dk, D, 2.0), mat(H * dv, D)
+            tensors[p + "mix.g"], tensors[p + "mix.o"] = mat(H * dv, D), mat(D, H * dv)
+        elif layer["type"] == "channel_delta":
+            delta(p + "mix.", m, True)
+        else:
+            a = m["left"]
+            H, G, dk, dv = a["heads"], a["kv_heads"], a["dim"], a["vdim"]
+            lp = p + "mix.left."
+            tensors[lp + "q"], tensors[lp + "k"], tensors[lp + "v"], tensors[lp + "o"] = mat(H * dk, D, 2.0), mat(G * dk, D, 2.0), mat(G * dv, D), mat(D, H * dv)
+            delta(p + "mix.right.", m["right"], False)
+            tensors[lp + "out"], tensors[p + "mix.right.out"] = vec(D, 1.0, 0.2), vec(D, 1.0, 0.2)
+        mlp = layer.get("mlp")
+        if not mlp:
+            continue
+        tensors[p + "norm2"] = vec(D, 1.0, 0.1)
+        if mlp["kind"] == "dense":
+            tensors[p + "mlp.up"], tensors[p + "mlp.down"] = mat(mlp["ff"], D, 1.5), mat(D, mlp["ff"])
+        else:
+            r = mlp["router"]
+            outputs = r["experts"] + r.get("identity", 0)
+            tensors[p + "mlp.router"], tensors[p + "mlp.correction"] = mat(outputs, D, 2.0), vec(outputs, 0.0, 0.05)
+            for k in range(r["experts"]):
+                q = p + f"mlp.e{k}."
+                tensors[q + "gate"], tensors[q + "up"], tensors[q + "down"] = mat(mlp["expert"]["ff"], D, 2.0), mat(mlp["expert"]["ff"], D), mat(D, mlp["expert"]["ff"])
+    return tensors
+
+
+save_senurax = save_voluzen
