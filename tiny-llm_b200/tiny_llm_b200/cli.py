@@ -45,7 +45,9 @@ def _self_describing(args, device):
         from .models import model_class
         from .synthetic import senurax_config, synthetic_senurax
 
-        config = senurax_config(pattern=args.synthetic.partition(":")[2] or "RdCmCdPm")
+        pattern = args.synthetic.partition(":")[2] or "CdPmRmCn"
+        count = len(pattern) // 2
+        config = senurax_config(pattern=pattern, loop=(min(1, count - 1), count, 2))  # all layers but the first run twice
         return model_class("Senurax").from_checkpoint(config, synthetic_senurax(config, seed=0), device=device, dtype=dtype)
     if args.model and "architecture" in json.loads((Path(args.model) / "config.json").read_text()):
         from .models import load_model

@@ -348,7 +348,7 @@ save_bapovik = save_voluzen  # the same directory layout: config.json + model.sa
 
 
 # ---- Senurax (retention / gated delta rule / softmax attention beside a delta rule, looped layers; senurax.py) -------
-def senurax_config(*, width=96, vocab=200, pattern="RdCmCdPm", loop=(1, 3, 2), heads=4, kv_heads=2, dim=16, vdim=24, rot_dims=8, rot_base=10000.0,
+def senurax_config(*, width=96, vocab=200, pattern="CdPmRmCn", loop=(1, 3, 2), heads=4, kv_heads=2, dim=16, vdim=24, rot_dims=8, rot_base=10000.0,
                    rot_factor=2.0, scale=None, rec_heads=4, rec_key_heads=2, rec_dim=16, rec_vdim=32, taps=4, ret_heads=2, ret_dim=16, ret_vdim=32,
                    ret_rot_dims=16, decay=None, ff=160, experts=6, identity=2, top=2, expert_ff=40, router_scale=1.5, softcap=20.0, eps=1e-5) -> dict:
     """A config.json for a stack spelled by ``pattern``, two letters a layer: the mixer (``R`` retention, ``C`` gated delta
