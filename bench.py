@@ -35,6 +35,9 @@ Numbers on the JSON line (decode):
   --workload voluzen  (not a BASELINE config) the Voluzen design - latent attention + mixture of experts, bf16 weights - at
             two sizes beside Qwen3 W4A16 of equal width / depth / heads / active feed-forward width: prefill and decode tok/s,
             and the design's kernels alone against the measured peaks; its own JSON line
+  --workload senurax  (not a BASELINE config) the Senurax design - retention, gated delta rule and rotated attention mixers,
+                      looped layers, experts with identity experts - at a few real-layer sizes beside Bapovik of equal size, and its
+                      kernels against their rooflines.
   --workload bapovik  (not a BASELINE config) the Bapovik design - windowed / chunked attention beside a recurrent mixer, experts,
             bf16 weights - at two sizes beside Voluzen of equal size, and the design's kernels alone against the measured peaks
   cpu_baseline  the reference's CPU path (oracle.model: dense bf16 weights, readable operators) on the
@@ -1189,13 +1192,230 @@ def run_bapovik(args) -> None:
                       "steps": steps, "warmup": max(args.warmup, 3), "peaks": measured_peaks(), "clocks": clocks, "sizes": results}), flush=True)
 
 
+# ------------------------------------------------------------------ workload: senurax (retention / gated delta rule / rotated attention + experts, beside Bapovik of equal size)
+SENURAX_SIZES = {
+    # four layer runs at sizes that resemble real models of this kind: a retention layer with a dense feed-forward, a delta-rule
+    # layer with per-channel decay and two parallel layers (rotated causal attention beside a delta rule) with experts; layers 1-2
+    # are entered through the loop's mixing product (one pass).  The Bapovik arm (the framework's closest model: fp32 stream,
+    # attention beside a recurrent mixer with state slots, experts, the same ragged step) has the same width, depth, head counts,
+    # head sizes and expert count; its ungated experts have 3/2 of the width, so that an expert has the same number of weights.
+    "w1024": dict(width=1024, vocab=32768, pattern="RdCmPmPm", loop=(1, 3, 1), heads=8, kv_heads=2, dim=96, vdim=64, rot_dims=48, rot_factor=4.0,
+                  rec_heads=8, rec_key_heads=4, rec_dim=64, rec_vdim=128, taps=4, ret_heads=8, ret_dim=64, ret_vdim=128, ret_rot_dims=64, ff=1536,
+                  experts=16, identity=2, top=2, expert_ff=512),
+    "w2048": dict(width=2048, vocab=32768, pattern="RdCmPmPm", loop=(1, 3, 1), heads=16, kv_heads=4, dim=192, vdim=128, rot_dims=96, rot_factor=4.0,
+                  rec_heads=16, rec_key_heads=8, rec_dim=64, rec_vdim=128, taps=4, ret_heads=16, ret_dim=64, ret_vdim=128, ret_rot_dims=64, ff=8192,
+                  experts=64, identity=4, top=6, expert_ff=1408),
+}
+
+
+def _senurax_kernels(cfg: dict, device, prompt: int, batch: int, context: int) -> dict:
+    """The kernels the design added, alone at this size, CUDA-event timed after warm-up, each against the roofline of its
+    kind (measured copy bandwidth for the scans and row kernels, measured cuBLAS bf16 burst for contractions); between
+    repetitions a 256 MB buffer is rewritten to flush L2."""
+    from extensions_b200.tiny_llm_ext_b200 import blocks
+
+    peaks = measured_peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    bf = torch.bfloat16
+
+    def timed(fn, reps=5):
+        for _ in range(3):
+            fn()
+        best = []
+        for _ in range(reps):
+            flush.fill_(1)
+            best.append(cuda_time_ms(fn))
+        return statistics.median(best)
+
+    def stream(nbytes, ms, **more):
+        return dict(more, ms=round(ms, 4), gbs=round(nbytes / ms / 1e6, 1), of_measured_hbm=round(nbytes / ms / 1e6 / peaks["hbm_gbs"], 4))
+
+    out = {}
+    H, G, dk, dv, K = cfg["rec_heads"], cfg["rec_key_heads"], cfg["rec_dim"], cfg["rec_vdim"], cfg["taps"]
+    C = 2 * G * dk + H * dv
+
+    def delta(tokens_per_seq, seqs, start, per_channel):
+        T = tokens_per_seq * seqs
+        q, k = (torch.randn((T, G, dk), device=device).to(bf) for _ in range(2))
+        v, beta = torch.randn((T, H, dv), device=device).to(bf), torch.randn((T, H), device=device).to(bf)
+        a = torch.randn((T, H * dk), device=device) if per_channel else torch.randn((T, H), device=device).to(bf)
+        a_log, dt = torch.zeros(H, device=device).to(bf), torch.zeros(H * dk if per_channel else H, device=device).to(bf)
+        info = torch.tensor([(s * tokens_per_seq, tokens_per_seq, start, s) for s in range(seqs)], dtype=torch.int32, device=device)
+        state = torch.zeros((seqs, H, dk, dv), device=device)
+        return timed(lambda: blocks.delta_scan(q, k, v, beta, a, a_log, dt, per_channel=per_channel, q_scale=dk ** -0.5, seq_info=info, state=state))
+
+    for per_channel, label in ((False, "head_decay"), (True, "channel_decay")):
+        ms = delta(prompt, 1, 0, per_channel)
+        nbytes = prompt * (2 * G * dk * 2 + H * dv * 2 + H * dv * 4 + (H * dk * 4 if per_channel else H * 2))
+        out[f"delta_scan_prefill_{label}"] = stream(nbytes, ms, tokens=prompt, us_per_token=round(ms * 1e3 / prompt, 3), gflops=round(7.0 * prompt * H * dk * dv / ms / 1e6, 1),
+                                                    note="one walk in token order per (head, 32 state columns): bound by the chain of dependent steps, not bytes")
+        ms = delta(1, batch, context, per_channel)
+        out[f"delta_scan_decode_{label}"] = stream(batch * H * dk * dv * 4 * 2, ms, batch=batch)
+
+    def conv(tokens_per_seq, seqs, start):
+        T = tokens_per_seq * seqs
+        x, taps = torch.randn((T, C), device=device).to(bf), torch.randn((C, K), device=device).to(bf)
+        info = torch.tensor([(s * tokens_per_seq, tokens_per_seq, start, s) for s in range(seqs)], dtype=torch.int32, device=device)
+        state = torch.zeros((seqs, C, K - 1), device=device)
+        return timed(lambda: blocks.short_conv(x, taps, seq_info=info, state=state, max_tokens=tokens_per_seq))
+
+    big = 32768  # tokens: input + output larger than L2
+    ms = conv(big, 1, 0)
+    out["short_conv_prefill"] = stream(big * C * 2 * 2, ms, tokens=big, channels=C)
+    ms = conv(1, batch, context)
+    out["short_conv_decode"] = stream(batch * C * (2 * 2 + (K - 1) * 4 * 2), ms, batch=batch)
+
+    RH, rk, rv, rot = cfg["ret_heads"], cfg["ret_dim"], cfg["ret_vdim"], cfg["ret_rot_dims"]
+
+    def retention(tokens_per_seq, seqs, start):
+        T = tokens_per_seq * seqs
+        q, k = (torch.randn((T, RH, rk), device=device).to(bf) for _ in range(2))
+        v = torch.randn((T, RH, rv), device=device).to(bf)
+        pos = torch.cat([torch.arange(start, start + tokens_per_seq, dtype=torch.int32) for _ in range(seqs)]).to(device)
+        tables = blocks.rope_table(pos, dims=rot, base=1e6)
+        decay = torch.linspace(0.97, 0.9995, RH, device=device)
+        info = torch.tensor([(s * tokens_per_seq, tokens_per_seq, start, s) for s in range(seqs)], dtype=torch.int32, device=device)
+        state = torch.zeros((seqs, RH, rk, rv), device=device)
+        return timed(lambda: blocks.decay_scan(q, k, v, None, None, q_scale=rk ** -0.5, seq_info=info, state=state, max_tokens=tokens_per_seq, head_decay=decay,
+                                               rope=tables, rope_dims=rot))
+
+    ms = retention(prompt, 1, 0)
+    nbytes = prompt * RH * (2 * rk * 2 + rv * 2 + rv * 4) + prompt * rot * 4
+    out["retention_scan_prefill"] = stream(nbytes, ms, tokens=prompt, us_per_token=round(ms * 1e3 / prompt, 3), gflops=round(4.0 * prompt * RH * rk * rv / ms / 1e6, 1),
+                                           note="decay_scan with a fixed decay per head and the rotation fused into its staging; three launches over 64-token segments")
+    ms = retention(1, batch, context)
+    out["retention_scan_decode"] = stream(batch * RH * rk * rv * 4 * 2, ms, batch=batch)
+
+    AH, AG, ak, av, page = cfg["heads"], cfg["kv_heads"], cfg["dim"], cfg["vdim"], 64
+    kernel, tile = blocks.paged_attention_kernel(bf, AH, AG, ak, av, page)
+
+    def attention(tokens_per_seq, seqs, ctx):
+        pages_per = -(-ctx // page)
+        slab = torch.randn((seqs * pages_per, page, AG * (ak + av)), dtype=torch.float32, device=device).to(bf)
+        table = torch.arange(seqs * pages_per, dtype=torch.int32, device=device).view(seqs, pages_per)
+        T = tokens_per_seq * seqs
+        pos = torch.cat([torch.arange(ctx - tokens_per_seq, ctx, dtype=torch.int32) for _ in range(seqs)]).to(device)
+        tiles = torch.tensor([(s * tokens_per_seq + f, min(tile, tokens_per_seq - f), s) for s in range(seqs) for f in range(0, tokens_per_seq, tile)],
+                             dtype=torch.int32, device=device)
+        q = torch.randn((T, AH, ak), dtype=torch.float32, device=device).to(bf)
+        o = torch.empty((T, AH, av), dtype=bf, device=device)
+        return timed(lambda: blocks.paged_attention(q, slab, table, tiles, pos, kv_heads=AG, dv=av, mask=blocks.MASK_CAUSAL, mask_size=0, scale=ak ** -0.5,
+                                                    out=o, kernel=kernel, max_context=ctx))
+
+    ms = attention(prompt, 1, prompt)
+    flops = 2.0 * AH * (ak + av) * prompt * (prompt + 1) / 2
+    out["causal_attention_prefill"] = {"kernel": kernel, "tokens": prompt, "ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1),
+                                       "of_measured_bf16_burst": round(flops / ms / 1e9 / peaks["bf16_tflops"], 4)}
+    ms = attention(1, batch, context)
+    out["causal_attention_decode"] = stream(batch * context * AG * (ak + av) * 2, ms, kernel=kernel, batch=batch, context=context)
+    x = torch.randn((big, AH * ak), device=device).to(bf)
+    pos = torch.arange(big, dtype=torch.int32, device=device)
+    ms = timed(lambda: blocks.rope_rows(x, pos, heads=AH, head_stride=ak, first=0, dims=cfg["rot_dims"], base=5e5, interleaved=True, factor=cfg["rot_factor"]))
+    out["rope_rows"] = stream(big * AH * cfg["rot_dims"] * 2 * 2, ms, rows=big)
+
+    D, E, ident, top, ff = cfg["width"], cfg["experts"], cfg["identity"], cfg["top"], cfg["expert_ff"]
+    g = torch.Generator(device="cpu").manual_seed(0)
+    h = torch.randn((prompt, D), generator=g).to(bf).to(device)
+    wg, wu = ((torch.randn((E, ff, D), device=device) / D**0.5).to(bf) for _ in range(2))
+    wd = (torch.randn((E, D, ff), device=device) / ff**0.5).to(bf)
+    router_w, bias = torch.randn((E + ident, D), device=device).to(bf), torch.zeros(E + ident, device=device).to(bf)
+    idx, gate = blocks.moe_route(h, router_w, None, top, blocks.SCORE_SOFTMAX_ALL, bias, 2.0)
+    real = float((idx < E).float().mean())
+    ms = timed(lambda: blocks.moe_experts(h, idx, gate, wg, wu, wd, blocks.ACT_SILU, None, identity=True))
+    flops = 2.0 * 3 * prompt * top * real * ff * D
+    out["moe_experts_prefill"] = {"tokens": prompt, "share_of_choices_on_real_experts": round(real, 3), "ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1),
+                                  "of_measured_bf16_burst": round(flops / ms / 1e9 / peaks["bf16_tflops"], 4)}
+    hb = h[:batch].contiguous()
+    idx, gate = blocks.moe_route(hb, router_w, None, top, blocks.SCORE_SOFTMAX_ALL, bias, 2.0)
+    ms = timed(lambda: blocks.moe_experts(hb, idx, gate, wg, wu, wd, blocks.ACT_SILU, None, identity=True))
+    touched = min(E, batch * top) * 3 * ff * D * 2
+    out["moe_experts_decode"] = {"batch": batch, "ms": round(ms, 4), "gbs_upper": round(touched / ms / 1e6, 1),
+                                 "of_measured_hbm_upper": round(touched / ms / 1e6 / peaks["hbm_gbs"], 4)}
+    ms = timed(lambda: blocks.moe_route(h, router_w, None, top, blocks.SCORE_SOFTMAX_ALL, bias, 2.0))
+    out["moe_route"] = {"tokens": prompt, "ms": round(ms, 4)}
+    rows = 65536  # > L2 in fp32
+    a, res = (torch.randn((rows, D), device=device) for _ in range(2))
+    w = torch.ones(D, device=device).to(bf)
+    ms = timed(lambda: blocks.add_norm(res, a, None, w, 1e-5))
+    out["add_norm"] = stream(rows * D * (4 + 4 + 4 + 2), ms, rows=rows)
+    return out
+
+
+def run_senurax(args) -> None:
+    """Prefill and decode throughput of the Senurax design at SENURAX_SIZES beside Bapovik (the framework's closest model)
+    of equal size, through the same ragged step; and the design's kernels against their rooflines.  One JSON line; random
+    weights, random prompts."""
+    from tiny_llm_b200.batch import greedy_tokens
+    from tiny_llm_b200.models import model_class
+    from tiny_llm_b200.ragged import RaggedEntry
+    from tiny_llm_b200.synthetic import bapovik_config, senurax_config, synthetic_bapovik, synthetic_senurax
+
+    device = torch.device("cuda:0")
+    prompt, batch, context, steps = args.prompt_len or 2048, 16, 1024, max(args.steps or 16, 4)
+    sampler = ClockSampler(0)
+    sampler.start()
+
+    def measure(model, vocab):
+        ids = synthetic_prompt(1, prompt, vocab)
+
+        def prefill_once():
+            cache = model.create_kv_cache()
+            model.forward_ragged([RaggedEntry(ids, cache)])
+            cache[0].release()
+
+        for _ in range(max(args.warmup, 3)):
+            prefill_once()
+        pre_ms = statistics.median(cuda_time_ms(prefill_once) for _ in range(5))
+        caches = [model.create_kv_cache() for _ in range(batch)]
+        for b, cache in enumerate(caches):
+            model.forward_ragged([RaggedEntry(synthetic_prompt(10 + b, context, vocab), cache)])
+        tokens = [1] * batch
+
+        def decode_step():
+            nonlocal tokens
+            logits = model.forward_ragged([RaggedEntry([t], c) for t, c in zip(tokens, caches)])
+            tokens = greedy_tokens(logits).tolist()  # the device -> host read a serving step makes
+
+        for _ in range(max(args.warmup, 3)):
+            decode_step()
+        torch.cuda.synchronize()
+        dec_ms = cuda_time_ms(lambda: [decode_step() for _ in range(steps)]) / steps
+        for cache in caches:
+            cache[0].release()
+        return {"prefill_ms": round(pre_ms, 3), "prefill_tok_s": round(prompt / pre_ms * 1e3, 1), "decode_ms_per_step": round(dec_ms, 3),
+                "decode_tok_s": round(batch / dec_ms * 1e3, 1)}
+
+    results = []
+    for name, size in SENURAX_SIZES.items():
+        config = senurax_config(**size)
+        model = model_class("Senurax").from_checkpoint(config, synthetic_senurax(config, seed=0), device=device, dtype=torch.bfloat16)
+        entry = {"size": name, "config": dict(size), "prompt_tokens": prompt, "decode_batch": batch, "decode_context": context,
+                 "senurax": measure(model, size["vocab"])}
+        entry["kernels"] = _senurax_kernels(size, device, prompt, batch, context)
+        del model
+        torch.cuda.empty_cache()
+        bsize = dict(width=size["width"], vocab=size["vocab"], pattern="APSP", heads=size["heads"], kv_heads=size["kv_heads"], dim=size["dim"], vdim=size["vdim"],
+                     window=prompt, chunk=prompt, softcap=30.0, rec_heads=size["rec_heads"], rec_dim=size["rec_dim"], rec_vdim=size["rec_vdim"], tau=16.0,
+                     experts=size["experts"], top=size["top"], expert_ff=size["expert_ff"] * 3 // 2)
+        bconfig = bapovik_config(**bsize)
+        other = model_class("Bapovik").from_checkpoint(bconfig, synthetic_bapovik(bconfig, seed=0), device=device, dtype=torch.bfloat16)
+        entry["bapovik_equal_size"] = dict(measure(other, size["vocab"]), config=bsize)
+        del other
+        torch.cuda.empty_cache()
+        results.append(entry)
+    clocks = sampler.stop()
+    print(json.dumps({"workload": "senurax", "metric": "Senurax prefill / decode tok/s beside Bapovik of equal size", "unit": UNIT, "n_gpus": 1,
+                      "dtype": "bf16 (unquantised weights in both)", "data": "synthetic (random weights, random prompts)",
+                      "steps": steps, "warmup": max(args.warmup, 3), "peaks": measured_peaks(), "clocks": clocks, "sizes": results}), flush=True)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", choices=sorted(METRICS) + ["voluzen", "bapovik"], default="decode")
+    ap.add_argument("--workload", choices=sorted(METRICS) + ["voluzen", "bapovik", "senurax"], default="decode")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the sweeps / secondary measurements under `extra`")
     ap.add_argument("--requests", type=int, default=0, help="serve/serve8k: total requests over all ranks")
@@ -1209,6 +1429,8 @@ def main() -> None:
         run_voluzen(args)
     elif args.workload == "bapovik":
         run_bapovik(args)
+    elif args.workload == "senurax":
+        run_senurax(args)
     elif args.impl == "reference":
         run_reference(args)
     elif args.workload == "decode":

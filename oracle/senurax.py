@@ -266,7 +266,9 @@ def forward(ids, weights, config, dtype=torch.float64, tap: list | None = None) 
 
 
 def greedy(ids, weights, config, new_tokens: int, dtype=torch.float64) -> list:
-    ids = list(ids)
+    """``new_tokens`` greedy tokens after the prompt, by recomputing the whole sequence for each."""
+    ids, out = list(ids), []
     for _ in range(new_tokens):
-        ids.append(int(forward(ids, weights, config, dtype)[-1].argmax()))
-    return ids
+        out.append(int(forward(ids, weights, config, dtype)[-1].argmax()))
+        ids.append(out[-1])
+    return out
