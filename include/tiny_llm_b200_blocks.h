@@ -162,11 +162,18 @@ int tlb_head_norm_gate(const float *o, const void *w, float eps, const void *gat
  *   (x / sqrt(sum x^2 + unit_eps)), q times q_scale.  per_channel: a [T, heads * dk] and dt_bias [heads * dk] give one decay
  *   per key channel; else a [T, heads], dt_bias [heads] one per head.  a is fp32 (a_is_f32) or `dtype`, rows a_token apart.
  * q, k [T, key_heads, dk] (head h reads key head h / (heads / key_heads)), v [T, heads, dv], beta [T, heads] rows b_token apart:
- * views in `dtype`, strides in elements.  seq_info, state slots and out as for tlb_decay_scan.  dk <= 256. */
+ * views in `dtype`, strides in elements.  seq_info, state slots and out as for tlb_decay_scan.  dk <= 256.
+ * max_tokens_per_seq = the largest token count in seq_info.  Up to TLB_DELTA_SCAN_SEGMENT tokens a sequence is walked in
+ * one go.  Longer portions are cut at the multiples of the segment length in absolute positions and run in three launches
+ * (every segment's end state from zero and its transition matrix [dk, dk], by the same walk started from the identity; the
+ * segments' start states in order; outputs per segment), which needs tlb_delta_scan_workspace(...) bytes. */
+#define TLB_DELTA_SCAN_SEGMENT 64
+size_t tlb_delta_scan_workspace(int num_seqs, int max_tokens_per_seq, int heads, int dk, int dv);
 int tlb_delta_scan(const void *q, long long q_token, long long q_head, const void *k, long long k_token, long long k_head, const void *v,
                    long long v_token, long long v_head, const void *beta, long long b_token, const void *a, int a_is_f32, long long a_token,
                    int per_channel, const void *a_log, const void *dt_bias, float q_scale, float unit_eps, int heads, int key_heads, int dk, int dv,
-                   const int32_t *seq_info, int num_seqs, float *state, long long slot_stride, int num_slots, float *out, int dtype, void *stream);
+                   const int32_t *seq_info, int num_seqs, int max_tokens_per_seq, float *state, long long slot_stride, int num_slots, float *out,
+                   void *workspace, size_t workspace_bytes, int dtype, void *stream);
 /* Short causal convolution along every sequence, per channel: y[t, c] = act(sum_i taps[c, K-1-i] x[t-i, c]) (act 1 = silu,
  * 0 = none), zeros before position 0.  x [T, channels] rows x_token apart, taps [channels, K] (K <= 8), y [T, channels]
  * contiguous.  The K-1 inputs before a step's first token live in the sequence's state slot (state + slot * slot_stride

@@ -127,29 +127,37 @@ def plain_delta(q, k, v, beta, a, a_log, dt_bias, per_channel):
 @pytest.mark.parametrize("per_channel", [False, True])
 @pytest.mark.parametrize("heads,key_heads,dk,dv", [(2, 2, 16, 32), (6, 2, 12, 40), (3, 1, 33, 7), (1, 1, 128, 64), (2, 1, 200, 36), (4, 4, 1, 5)])
 def test_delta_scan_against_the_recurrence_in_portions_batches_and_reused_slots(dev, dtype, per_channel, heads, key_heads, dk, dv):
-    T = 70
+    T = 200
     args = delta_inputs(T, heads, key_heads, dk, dv, per_channel, heads * dk + dv, dtype)
     want = plain_delta(*args, per_channel)
     q, k, v, beta, a, a_log, dt_bias = (t.to(dev) for t in args)
     state = torch.full((3, heads, dk, dv), 4.0, device=dev)  # stale numbers
     run = lambda lo, hi, si, a_in=a: blocks.delta_scan(q[lo:hi], k[lo:hi], v[lo:hi], beta[lo:hi], a_in[lo:hi], a_log, dt_bias, per_channel=per_channel,
-                                                      q_scale=dk ** -0.5, seq_info=si, state=state)
-    whole = run(0, T, info(dev, [0, T, 0, 1]))
-    close(whole, want, 5e-6 if dtype == torch.float32 else 2e-2)
-    kept = state[1].clone()
+                                                      q_scale=dk ** -0.5, seq_info=si, state=state, max_tokens=hi - lo)
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    walked = in_portions(dev, T, [64], 1, run)  # portions of up to a segment are one walk in token order
+    close(walked, want, tol)
+    kept = state[1].clone().cpu()
     for sizes in ([1], [2], [1, 2, 16, 17, 3, 31]):
         state.fill_(-2.0)
         got = in_portions(dev, T, sizes, 2, run)
-        assert torch.equal(got, whole), sizes  # one summation order whatever the cut
-        assert torch.equal(state[2], kept)
-    assert torch.equal(run(0, T, info(dev, [0, T, 0, 1]), a.float()), whole)  # the decay input as an fp32 accumulator
-    # two sequences at once, one continuing from its slot
+        assert torch.equal(got, walked), sizes  # one summation order whatever the cut
+        assert torch.equal(state[2].cpu(), kept)
+    assert torch.equal(in_portions(dev, T, [64], 1, lambda lo, hi, si: run(lo, hi, si, a.float())), walked)  # the decay input as an fp32 accumulator
+    # longer portions run as segments cut at absolute multiples of 64: the same up to the rounding of the combination
+    for sizes in ([T], [100, 100], [3, 150, 47], [63, 66, 71], [1, 199]):
+        state.fill_(7.0)
+        close(in_portions(dev, T, sizes, 0, run), want, tol)
+        close(state[0], kept, tol)
+    # a long sequence that continues from its slot beside a short new one, in one launch
     state.fill_(1.0)
     run(0, 30, info(dev, [0, 30, 0, 0]))
     cat = lambda t: torch.cat([t[:11], t[30:]])
     both = blocks.delta_scan(cat(q), cat(k), cat(v), cat(beta), cat(a), a_log, dt_bias, per_channel=per_channel, q_scale=dk ** -0.5,
-                             seq_info=info(dev, [[0, 11, 0, 1], [11, T - 30, 30, 0]]), state=state)
-    assert torch.equal(both[:11], whole[:11]) and torch.equal(both[11:], whole[30:])
+                             seq_info=info(dev, [[0, 11, 0, 1], [11, T - 30, 30, 0]]), state=state, max_tokens=T - 30)
+    assert torch.equal(both[:11], walked[:11])
+    close(both[11:], want[30:], tol)
+    close(state[0], kept, tol)
 
 
 def test_delta_rule_keeps_a_far_token_and_replaces_what_a_key_said_before(dev):

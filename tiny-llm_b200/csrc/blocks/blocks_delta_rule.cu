@@ -13,8 +13,14 @@
 // the two sums over rows (S^T k, S^T q) close with two shuffles each.  Tokens are staged 16 (8 for dk > 128) at a time
 // in shared memory as fp32: decay, unit k, scaled unit q per key channel, all computed there in fp32 from the
 // projections.  A sequence that starts at position 0 starts from zero, whatever its slot held; the slot is written back
-// after the last token.  Every sum has an order fixed by token and channel indices alone, so a token's result does not
-// depend on how the sequence was cut into steps or on what else is in the batch.
+// after the last token.  Single tokens and portions of up to 64 tokens are one walk, whose sums have an order fixed by token
+// and channel indices alone.  A longer portion is cut into segments at the multiples of 64 in ABSOLUTE positions, which run
+// side by side.  The state after a segment is linear in the state before it, S_end = P S_start + L with P [dk, dk] the
+// product of the tokens' transitions (I - beta k k^T) diag(g) and L the end state from zero, and the columns of P come out of
+// the same walk started from the identity with zero values.  So: every segment's L and P (pass 1), the segments' start
+// states by walking those in order (delta_combine_kernel), then the outputs of every segment from its start state (pass
+// 3).  The cuts depend on positions only, so how a prompt was cut into steps changes a result by the rounding of the
+// combination at most.
 #include "blocks_common.cuh"
 
 namespace tlb {
@@ -22,7 +28,29 @@ namespace tlb {
 constexpr int kDrCols = 32;   // state columns per CTA
 constexpr int kDrLanes = 4;   // lanes per column
 
+constexpr int kDrSegment = TLB_DELTA_SCAN_SEGMENT;  // positions per segment of a long portion
+
 __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+
+// Segment c of a sequence's new tokens [p0, p0 + n), cut at the multiples of kDrSegment in absolute positions; a portion of
+// at most one segment's length is never cut.  Returns false when the sequence has no segment c.
+__device__ __forceinline__ bool dr_segment(int p0, int n, int c, int &lo, int &hi, int &nseg) {
+    const int end = p0 + n, b0 = (p0 / kDrSegment + 1) * kDrSegment;
+    nseg = (n <= kDrSegment || end <= b0) ? 1 : 1 + (end - b0 + kDrSegment - 1) / kDrSegment;
+    if (c >= nseg) return false;
+    lo = c == 0 ? p0 : b0 + (c - 1) * kDrSegment;
+    hi = nseg == 1 ? end : min(end, c == 0 ? b0 : lo + kDrSegment);
+    return true;
+}
+
+// One kernel, three uses (pass):
+//   0  the whole portion of a sequence in one CTA per (head, column block): state from the slot (or zero at position 0),
+//      outputs, state back to the slot.
+//   1  segment c alone, no outputs.  Column blocks below `colblocks` walk the value columns from a ZERO state (L); the
+//      blocks after them walk the dk columns of the identity with zero values (P).  Both go to the workspace; the last
+//      segment of a sequence is skipped (nobody needs what follows it).
+//   3  segment c from the start state that delta_combine_kernel left in the workspace: outputs; the last segment writes
+//      the slot.  A sequence of the launch that is short enough for one walk runs here as in pass 0.
 
 template <typename T, int KR /* rows per lane: dk <= 4 * KR */, int kTok /* tokens staged at a time */>
 __global__ void __launch_bounds__(kDrCols * kDrLanes)
@@ -30,20 +58,31 @@ delta_scan_kernel(const T *__restrict__ q, long long q_token, long long q_head, 
                   const T *__restrict__ v, long long v_token, long long v_head, const T *__restrict__ beta, long long b_token,
                   const void *__restrict__ a, int a_f32, long long a_token, int per_channel, const T *__restrict__ a_log,
                   const T *__restrict__ dt_bias, float q_scale, float unit_eps, int heads, int group, int dk, int dv,
-                  const int32_t *__restrict__ seq_info, float *__restrict__ state, long long slot_stride, int num_slots, float *__restrict__ out) {
+                  const int32_t *__restrict__ seq_info, float *__restrict__ state, long long slot_stride, int num_slots, float *__restrict__ out,
+                  int pass, int max_segments, float *__restrict__ seg_state, float *__restrict__ seg_trans) {
     __shared__ float4 sx[kTok * 4 * KR];  // per token and key channel: (decay, k, q, -)
     __shared__ float sv[kTok * kDrCols];
     __shared__ float sbeta[kTok];
     __shared__ float sinv[kTok * 2];
-    const int colblocks = (dv + kDrCols - 1) / kDrCols;
-    const int s = blockIdx.x, head = blockIdx.y / colblocks, col0 = (blockIdx.y % colblocks) * kDrCols;
-    const int first = seq_info[s * 4 + 0], count = seq_info[s * 4 + 1], start = seq_info[s * 4 + 2], slot = seq_info[s * 4 + 3];
+    const int colblocks = (dv + kDrCols - 1) / kDrCols, kblocks = (dk + kDrCols - 1) / kDrCols;
+    const int per_head = pass == 1 ? colblocks + kblocks : colblocks;
+    const int s = blockIdx.x, head = blockIdx.y / per_head, block = blockIdx.y % per_head, c = blockIdx.z;
+    const bool trans = block >= colblocks;  // pass 1 only: a block of columns of the identity
+    const int col0 = (trans ? block - colblocks : block) * kDrCols, width = trans ? dk : dv;
+    const int seq_first = seq_info[s * 4 + 0], seq_count = seq_info[s * 4 + 1], start = seq_info[s * 4 + 2], slot = seq_info[s * 4 + 3];
+    int lo = start, hi = start + seq_count, nseg = 1;
+    if (pass != 0 && !dr_segment(start, seq_count, c, lo, hi, nseg)) return;
+    if (pass == 1 && c == nseg - 1) return;
+    const bool whole = pass == 0 || (pass == 3 && nseg == 1);  // a short portion in a launch with long ones runs as in pass 0
+    const int first = seq_first + (lo - start), count = hi - lo;
     const int cidx = threadIdx.x / kDrLanes, r = threadIdx.x % kDrLanes;
     const int col = col0 + cidx;
-    const bool col_ok = col < dv;
+    const bool col_ok = col < width;
     const bool slot_ok = slot >= 0 && slot < num_slots;
     const int khead = head / group;
     float *mine = state + (size_t)(slot_ok ? slot : 0) * slot_stride + (size_t)head * dk * dv;
+    const size_t seg_index = ((size_t)s * max_segments + c) * heads + head;
+    float *seg = seg_state ? seg_state + seg_index * dk * dv : nullptr;
     const float rate = expf(to_f(a_log[head]));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -51,7 +90,10 @@ delta_scan_kernel(const T *__restrict__ q, long long q_token, long long q_head, 
 #pragma unroll
     for (int i = 0; i < KR; ++i) {
         int row = r + kDrLanes * i;
-        S[i] = (start > 0 && slot_ok && col_ok && row < dk) ? mine[(size_t)row * dv + col] : 0.f;
+        bool ok = col_ok && row < dk;
+        if (whole) S[i] = (start > 0 && slot_ok && ok) ? mine[(size_t)row * dv + col] : 0.f;
+        else if (pass == 1) S[i] = (trans && ok && row == col) ? 1.f : 0.f;
+        else S[i] = ok ? seg[(size_t)row * dv + col] : 0.f;
     }
     for (int t0 = 0; t0 < count; t0 += kTok) {
         const int n = min(kTok, count - t0);
@@ -66,7 +108,7 @@ delta_scan_kernel(const T *__restrict__ q, long long q_token, long long q_head, 
         }
         for (int e = threadIdx.x; e < n * kDrCols; e += blockDim.x) {
             int j = e / kDrCols, d = e - j * kDrCols;
-            sv[e] = col0 + d < dv ? to_f(v[(size_t)(first + t0 + j) * v_token + (size_t)head * v_head + col0 + d]) : 0.f;
+            sv[e] = (!trans && col0 + d < dv) ? to_f(v[(size_t)(first + t0 + j) * v_token + (size_t)head * v_head + col0 + d]) : 0.f;
         }
         if (threadIdx.x < n) {
             float bl = to_f(beta[(size_t)(first + t0 + threadIdx.x) * b_token + head]);
@@ -129,18 +171,97 @@ delta_scan_kernel(const T *__restrict__ q, long long q_token, long long q_head, 
                     o1 = fmaf(x.z, S[i + 1], o1);
                 }
             }
-            float o = o0 + o1;
-            o += __shfl_xor_sync(0xffffffffu, o, 1);
-            o += __shfl_xor_sync(0xffffffffu, o, 2);
-            if (r == 0 && col_ok) out[((size_t)(first + t0 + j) * heads + head) * dv + col] = o;
+            if (pass != 1) {
+                float o = o0 + o1;
+                o += __shfl_xor_sync(0xffffffffu, o, 1);
+                o += __shfl_xor_sync(0xffffffffu, o, 2);
+                if (r == 0 && col_ok) out[((size_t)(first + t0 + j) * heads + head) * dv + col] = o;
+            }
         }
     }
-    if (slot_ok && col_ok) {
+    // where the end state goes: the slot (the whole portion, or its last segment), or the workspace (L or P of a segment)
+    float *dst = nullptr;
+    if (pass == 1) dst = trans ? seg_trans + seg_index * dk * dk : seg;
+    else if ((whole || c == nseg - 1) && slot_ok) dst = mine;
+    if (dst != nullptr && col_ok) {
 #pragma unroll
         for (int i = 0; i < KR; ++i) {
             int row = r + kDrLanes * i;
-            if (row < dk) mine[(size_t)row * dv + col] = S[i];
+            if (row < dk) dst[trans ? (size_t)col * dk + row : (size_t)row * dv + col] = S[i];  // P goes out transposed: Pt[j][row]
         }
+    }
+}
+
+// Between the two passes: walk a sequence's segments in order, S_start[c + 1] = P[c] S_start[c] + L[c], and leave every
+// segment's START state where its L was.  One CTA per (sequence, head, 32 state columns): the columns never mix.  The
+// CTA keeps its 32 columns of S in shared memory, lanes = columns; pass 1 stored P transposed (Pt[j][row]), so with the
+// segment's Pt staged in shared memory a warp takes four rows at a time from one 16-byte broadcast read per j; every sum
+// runs over j in order.  STAGE = false (dk too large for shared memory) reads Pt from global memory instead.
+constexpr int kDcThreads = 256;
+
+template <bool STAGE>
+__global__ void __launch_bounds__(kDcThreads)
+delta_combine_kernel(const int32_t *__restrict__ seq_info, const float *__restrict__ state, long long slot_stride, int num_slots, int heads, int dk,
+                     int dv, int max_segments, float *__restrict__ seg_state, const float *__restrict__ seg_trans) {
+    extern __shared__ float4 combine_smem[];
+    const int dkp = (dk + 3) & ~3;                   // rows padded to whole groups of four
+    float *cur = (float *)combine_smem, *nxt = cur + dkp * kDrCols, *pt = nxt + dkp * kDrCols;  // [dkp][32] x 2, then Pt [dk][dkp]
+    const int colblocks = (dv + kDrCols - 1) / kDrCols;
+    const int s = blockIdx.x, head = blockIdx.y / colblocks, col0 = (blockIdx.y % colblocks) * kDrCols;
+    const int count = seq_info[s * 4 + 1], start = seq_info[s * 4 + 2], slot = seq_info[s * 4 + 3];
+    int lo, hi, nseg;
+    dr_segment(start, count, 0, lo, hi, nseg);
+    if (nseg <= 1) return;
+    const bool slot_ok = slot >= 0 && slot < num_slots;
+    const float *mine = state + (size_t)(slot_ok ? slot : 0) * slot_stride + (size_t)head * dk * dv;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, col = col0 + lane, warps = kDcThreads / 32;
+    const bool col_ok = col < dv;
+    for (int row = warp; row < dkp; row += warps)
+        cur[row * kDrCols + lane] = (row < dk && start > 0 && slot_ok && col_ok) ? mine[(size_t)row * dv + col] : 0.f;
+    __syncthreads();
+    for (int c = 0; c < nseg; ++c) {
+        const size_t idx = ((size_t)s * max_segments + c) * heads + head;
+        float *cell = seg_state + idx * dk * dv;
+        const float *gpt = seg_trans + idx * dk * dk;  // Pt[j * dk + row]
+        const bool last = c == nseg - 1;
+        if (STAGE && !last) {
+            for (int e = threadIdx.x; e < dk * dkp; e += kDcThreads) {
+                int j = e / dkp, row = e - j * dkp;
+                pt[e] = row < dk ? gpt[(size_t)j * dk + row] : 0.f;
+            }
+            __syncthreads();
+        }
+        for (int g4 = warp * 4; g4 < dkp; g4 += warps * 4) {
+            float local[4], acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int row = g4 + i;
+                const bool ok = row < dk && col_ok;
+                local[i] = (!last && ok) ? cell[(size_t)row * dv + col] : 0.f;
+                if (ok) cell[(size_t)row * dv + col] = cur[row * kDrCols + lane];  // the segment's start state
+            }
+            if (last) continue;
+            for (int j = 0; j < dk; ++j) {
+                const float x = cur[j * kDrCols + lane];
+                if (STAGE) {
+                    const float4 p = *reinterpret_cast<const float4 *>(pt + j * dkp + g4);
+                    acc[0] = fmaf(p.x, x, acc[0]);
+                    acc[1] = fmaf(p.y, x, acc[1]);
+                    acc[2] = fmaf(p.z, x, acc[2]);
+                    acc[3] = fmaf(p.w, x, acc[3]);
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        if (g4 + i < dk) acc[i] = fmaf(gpt[(size_t)j * dk + g4 + i], x, acc[i]);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) nxt[(g4 + i) * kDrCols + lane] = acc[i] + local[i];
+        }
+        __syncthreads();
+        float *t = cur;
+        cur = nxt;
+        nxt = t;
     }
 }
 
@@ -214,25 +335,66 @@ using namespace tlb;
 
 extern "C" {
 
+size_t tlb_delta_scan_workspace(int num_seqs, int max_tokens_per_seq, int heads, int dk, int dv) {
+    if (max_tokens_per_seq <= kDrSegment) return 0;
+    size_t segs = (size_t)num_seqs * (2 + (max_tokens_per_seq - 1) / kDrSegment);
+    return segs * heads * ((size_t)dk * dv + (size_t)dk * dk) * sizeof(float);
+}
+
 int tlb_delta_scan(const void *q, long long q_token, long long q_head, const void *k, long long k_token, long long k_head, const void *v,
                    long long v_token, long long v_head, const void *beta, long long b_token, const void *a, int a_is_f32, long long a_token,
                    int per_channel, const void *a_log, const void *dt_bias, float q_scale, float unit_eps, int heads, int key_heads, int dk, int dv,
-                   const int32_t *seq_info, int num_seqs, float *state, long long slot_stride, int num_slots, float *out, int dtype, void *stream) {
+                   const int32_t *seq_info, int num_seqs, int max_tokens_per_seq, float *state, long long slot_stride, int num_slots, float *out,
+                   void *workspace, size_t workspace_bytes, int dtype, void *stream) {
     if (num_seqs <= 0) return TL_OK;
     if (!q || !k || !v || !beta || !a || !a_log || !dt_bias || !seq_info || !state || !out || heads <= 0 || key_heads <= 0 || heads % key_heads ||
-        dk <= 0 || dv <= 0 || num_slots <= 0)
+        dk <= 0 || dv <= 0 || num_slots <= 0 || max_tokens_per_seq <= 0)
         return tl::fail(TL_EINVAL, "delta_scan: bad argument");
     if (dk > 256) return tl::fail(TL_EINVAL, "delta_scan: key size %d > 256", dk);
-    const int colblocks = ceil_div(dv, kDrCols), group = heads / key_heads;
+    // portions longer than a segment are cut at absolute multiples of the segment length and run in three passes
+    const bool segmented = max_tokens_per_seq > kDrSegment;
+    const int max_segments = segmented ? 2 + (max_tokens_per_seq - 1) / kDrSegment : 1;
+    float *seg_state = nullptr, *seg_trans = nullptr;
+    if (segmented) {
+        if (!workspace || workspace_bytes < tlb_delta_scan_workspace(num_seqs, max_tokens_per_seq, heads, dk, dv))
+            return tl::fail(TL_EWORKSPACE, "delta_scan: workspace missing or too small");
+        seg_state = (float *)workspace;
+        seg_trans = seg_state + (size_t)num_seqs * max_segments * heads * dk * dv;
+    }
+    const int colblocks = ceil_div(dv, kDrCols), kblocks = ceil_div(dk, kDrCols), group = heads / key_heads;
     cudaStream_t st = as_stream(stream);
     const int kr = ceil_div(dk, kDrLanes);
-#define TLB_DR_K(KRV)                                                                                                                              \
-    delta_scan_kernel<T, KRV, (KRV > 32 ? 8 : 16)><<<dim3(num_seqs, heads * colblocks), kDrCols * kDrLanes, 0, st>>>(                               \
+#define TLB_DR_K(KRV, PASS, GY, GZ)                                                                                                                 \
+    delta_scan_kernel<T, KRV, (KRV > 32 ? 8 : 16)><<<dim3(num_seqs, heads * (GY), GZ), kDrCols * kDrLanes, 0, st>>>(                                \
         (const T *)q, q_token, q_head, (const T *)k, k_token, k_head, (const T *)v, v_token, v_head, (const T *)beta, b_token, a, a_is_f32, a_token, \
-        per_channel, (const T *)a_log, (const T *)dt_bias, q_scale, unit_eps, heads, group, dk, dv, seq_info, state, slot_stride, num_slots, out)
-    TLB_DISPATCH(dtype, "delta_scan", if (kr <= 8) TLB_DR_K(8); else if (kr <= 16) TLB_DR_K(16); else if (kr <= 32) TLB_DR_K(32); else TLB_DR_K(64));
+        per_channel, (const T *)a_log, (const T *)dt_bias, q_scale, unit_eps, heads, group, dk, dv, seq_info, state, slot_stride, num_slots, out,    \
+        PASS, max_segments, seg_state, seg_trans)
+#define TLB_DR(PASS, GY, GZ)                                                                                                                       \
+    TLB_DISPATCH(dtype, "delta_scan", if (kr <= 8) TLB_DR_K(8, PASS, GY, GZ); else if (kr <= 16) TLB_DR_K(16, PASS, GY, GZ);                        \
+                 else if (kr <= 32) TLB_DR_K(32, PASS, GY, GZ); else TLB_DR_K(64, PASS, GY, GZ))
+    if (!segmented) {
+        TLB_DR(0, colblocks, 1);
+        TL_LAUNCH_CHECK("delta_scan");
+        return TL_OK;
+    }
+    TLB_DR(1, colblocks + kblocks, max_segments);
+    TL_LAUNCH_CHECK("delta_scan (local states and transitions)");
+    const int dkp = (dk + 3) & ~3;
+    const size_t states = (size_t)2 * dkp * kDrCols * sizeof(float), staged = states + (size_t)dk * dkp * sizeof(float);
+    const bool stage = staged <= 160 * 1024;
+    const size_t smem = stage ? staged : states;
+    auto combine = stage ? delta_combine_kernel<true> : delta_combine_kernel<false>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(combine, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return tl::fail(TL_ECUDA, "delta_scan: %s", cudaGetErrorString(e));
+    }
+    combine<<<dim3(num_seqs, heads * colblocks), kDcThreads, smem, st>>>(seq_info, state, slot_stride, num_slots, heads, dk, dv, max_segments, seg_state,
+                                                                       seg_trans);
+    TL_LAUNCH_CHECK("delta_scan (combine)");
+    TLB_DR(3, colblocks, max_segments);
+    TL_LAUNCH_CHECK("delta_scan (outputs)");
+#undef TLB_DR
 #undef TLB_DR_K
-    TL_LAUNCH_CHECK("delta_scan");
     return TL_OK;
 }
 

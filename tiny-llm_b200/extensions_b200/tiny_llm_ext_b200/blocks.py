@@ -53,8 +53,9 @@ _SIGNATURES = {
     "tlb_decay_scan_workspace": (ctypes.c_size_t, [_I, _I, _I, _I, _I]),
     "tlb_decay_scan": (_I, [_VP, _LL, _LL, _VP, _LL, _LL, _VP, _LL, _LL, _VP, _LL, _VP, _F, _VP, _VP, _VP, _I, _I, _F, _I, _I, _I, _VP, _I, _I, _VP, _LL, _I,
                             _VP, _VP, ctypes.c_size_t, _I, _VP]),
-    "tlb_delta_scan": (_I, [_VP, _LL, _LL, _VP, _LL, _LL, _VP, _LL, _LL, _VP, _LL, _VP, _I, _LL, _I, _VP, _VP, _F, _F, _I, _I, _I, _I, _VP, _I, _VP, _LL, _I,
-                            _VP, _I, _VP]),
+    "tlb_delta_scan_workspace": (ctypes.c_size_t, [_I, _I, _I, _I, _I]),
+    "tlb_delta_scan": (_I, [_VP, _LL, _LL, _VP, _LL, _LL, _VP, _LL, _LL, _VP, _LL, _VP, _I, _LL, _I, _VP, _VP, _F, _F, _I, _I, _I, _I, _VP, _I, _I, _VP, _LL,
+                            _I, _VP, _VP, ctypes.c_size_t, _I, _VP]),
     "tlb_short_conv": (_I, [_VP, _LL, _VP, _I, _I, _I, _VP, _I, _I, _VP, _LL, _I, _VP, _I, _VP]),
     "tlb_act_rows": (_I, [_VP, _VP, _I, _I, _I, _I, _VP]),
     "tlb_softcap_rows": (_I, [_VP, _I, _I, _F, _VP]),
@@ -553,10 +554,12 @@ def head_norm_gate(o, weight, eps: float, gate=None, act: int = 1):
     return out
 
 
-def delta_scan(q, k, v, beta, a, a_log, dt_bias, *, per_channel: bool, q_scale: float, unit_eps: float = 1e-6, seq_info, state, out=None):
+def delta_scan(q, k, v, beta, a, a_log, dt_bias, *, per_channel: bool, q_scale: float, unit_eps: float = 1e-6, seq_info, state, out=None,
+               max_tokens: int | None = None):
     """Gated delta rule: ``q, k [T, G, dk]``, ``v [T, H, dv]``, ``beta [T, H]`` (logits) views in one dtype; ``a`` the decay
     input, ``[T, H]`` (one decay per head, ``dt_bias [H]``) or ``[T, H * dk]`` (one per key channel, ``dt_bias [H * dk]``),
-    fp32 or that dtype; ``a_log [H]``; ``state [slots, H, dk, dv]`` fp32 -> fp32 ``[T, H, dv]``."""
+    fp32 or that dtype; ``a_log [H]``; ``state [slots, H, dk, dv]`` fp32 -> fp32 ``[T, H, dv]``.  ``max_tokens``: the largest
+    count in ``seq_info`` (default: all tokens); portions longer than a segment run as parallel segments over a workspace."""
     _gpu("delta_scan", q, k, v, beta, a, a_log, dt_bias, seq_info, state, out)
     _contig("delta_scan", a_log, dt_bias, seq_info)
     T, G, dk = q.shape
@@ -575,10 +578,14 @@ def delta_scan(q, k, v, beta, a, a_log, dt_bias, *, per_channel: bool, q_scale: 
         raise RuntimeError("delta_scan: seq_info must be int32 [S, 4]")
     if out is None:
         out = torch.empty((T, H, dv), dtype=torch.float32, device=q.device)
-    _check(library().tlb_delta_scan(_ptr(q), q.stride(0), q.stride(1), _ptr(k), k.stride(0), k.stride(1), _ptr(v), v.stride(0), v.stride(1), _ptr(beta),
-                                    beta.stride(0), _ptr(a), int(a.dtype == torch.float32), a.stride(0), int(per_channel), _ptr(a_log), _ptr(dt_bias),
-                                    float(q_scale), float(unit_eps), H, G, dk, dv, _ptr(seq_info), seq_info.shape[0], _ptr(state), state.stride(0),
-                                    state.shape[0], _ptr(out), _code(q.dtype), _stream(q)))
+    longest = T if max_tokens is None else max(1, min(int(max_tokens), T))
+    lib = library()
+    nbytes = int(lib.tlb_delta_scan_workspace(seq_info.shape[0], longest, H, dk, dv))
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=q.device) if nbytes else None
+    _check(lib.tlb_delta_scan(_ptr(q), q.stride(0), q.stride(1), _ptr(k), k.stride(0), k.stride(1), _ptr(v), v.stride(0), v.stride(1), _ptr(beta),
+                              beta.stride(0), _ptr(a), int(a.dtype == torch.float32), a.stride(0), int(per_channel), _ptr(a_log), _ptr(dt_bias),
+                              float(q_scale), float(unit_eps), H, G, dk, dv, _ptr(seq_info), seq_info.shape[0], longest, _ptr(state), state.stride(0),
+                              state.shape[0], _ptr(out), _ptr(ws), nbytes, _code(q.dtype), _stream(q)))
     return out
 
 

@@ -68,5 +68,6 @@ class GatedDeltaRule:
         if self.w_g2 is not None:
             gate = linear(gate.contiguous(), self.w_g2)
         o = blocks.delta_scan(q.unflatten(1, (G, dk)), k.unflatten(1, (G, dk)), v.unflatten(1, (H, dv)), beta, a, self.a_log, self.dt_bias,
-                              per_channel=self.channel_decay, q_scale=dk ** -0.5, unit_eps=1e-6, seq_info=plan.seq_info, state=state)
+                              per_channel=self.channel_decay, q_scale=dk ** -0.5, unit_eps=1e-6, seq_info=plan.seq_info, state=state,
+                              max_tokens=plan.max_tokens)
         return linear_wide(blocks.head_norm_gate(o, self.norm_weight, self.eps, gate, act=self.gate_act), self.w_o)
