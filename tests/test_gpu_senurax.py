@@ -19,7 +19,6 @@ from extensions_b200.tiny_llm_ext_b200 import blocks
 from tiny_llm_b200 import BatchingKvCache, ContinuousBatcher, greedy_generate_ids
 from tiny_llm_b200.mlp import MixtureOfExperts, TopKRouter
 from tiny_llm_b200.models import load_model, model_class
-from tiny_llm_b200.paged_attention import PagedGroupedAttention
 from tiny_llm_b200.ragged import RaggedEntry
 from tiny_llm_b200.synthetic import save_senurax, senurax_config, synthetic_senurax
 
@@ -270,12 +269,13 @@ def test_rotated_attention_finds_one_key_far_away_and_at_page_borders(dev, kerne
     S = 300
     g = torch.Generator().manual_seed(9)
     w_o = torch.eye(H * dv).to(kernel_dtype).to(dev)
-    att = PagedGroupedAttention(heads=H, kv_heads=G, dim=dk, vdim=dv, scale=1.0, mask="causal", mask_size=0, w_o=w_o, page_size=page,
-                                rot={"dims": rot, "base": 100.0, "factor": 2.0, "interleaved": True})
     from tiny_llm_b200.latent_kv_cache import LatentPagedPool
+    from tiny_llm_b200.paged_attention import PagedGroupedAttention  # here, not at the top: the module shares its name with a function of the package
     from tiny_llm_b200.ragged import RaggedPlan
     from tiny_llm_b200.state_cache import HybridPagedCache
 
+    att = PagedGroupedAttention(heads=H, kv_heads=G, dim=dk, vdim=dv, scale=1.0, mask="causal", mask_size=0, w_o=w_o, page_size=page,
+                                rot={"dims": rot, "base": 100.0, "factor": 2.0, "interleaved": True})
     for target in (0, 31, 32, 33, 63, 64, 255, 256, 298, 299):
         q, k, v = 0.1 * torch.randn(S, H, dk, generator=g), 0.1 * torch.randn(S, G, dk, generator=g), torch.randn(S, G, dv, generator=g)
         q[S - 1, :, rot:] = 3.0   # the unrotated entries carry the match
