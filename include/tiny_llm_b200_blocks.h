@@ -175,7 +175,7 @@ int tlb_delta_scan(const void *q, long long q_token, long long q_head, const voi
                    const int32_t *seq_info, int num_seqs, int max_tokens_per_seq, float *state, long long slot_stride, int num_slots, float *out,
                    void *workspace, size_t workspace_bytes, int dtype, void *stream);
 /* Short causal convolution along every sequence, per channel: y[t, c] = act(sum_i taps[c, K-1-i] x[t-i, c]) (act 1 = silu,
- * 0 = none), zeros before position 0.  x [T, channels] rows x_token apart, taps [channels, K] (K <= 8), y [T, channels]
+ * 0 = none), zeros before position 0.  x [T, channels] rows x_token apart, taps [channels, K] (K <= 16), y [T, channels]
  * contiguous.  The K-1 inputs before a step's first token live in the sequence's state slot (state + slot * slot_stride
  * floats, [channels, K-1], oldest first) and are replaced by the step's last ones. */
 int tlb_short_conv(const void *x, long long x_token, const void *taps, int channels, int num_taps, int act, const int32_t *seq_info, int num_seqs,

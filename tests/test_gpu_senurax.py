@@ -76,7 +76,7 @@ def in_portions(dev, total, sizes, slot, fn):
 
 # ---------------------------------------------------------------------------------------------- mechanisms alone
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("channels,taps", [(40, 4), (7, 2), (130, 3), (16, 1), (9, 8)])
+@pytest.mark.parametrize("channels,taps", [(40, 4), (7, 2), (130, 3), (16, 1), (9, 8), (5, 16)])
 def test_short_convolution_in_portions_batches_and_reused_slots(dev, dtype, channels, taps):
     g = torch.Generator().manual_seed(channels + taps)
     T = 90
@@ -367,6 +367,9 @@ CONFIGS = {
                 identity=3, top=3, expert_ff=24, softcap=5.0),
     # no loop at all, one tap (no convolution state)
     "flat": dict(pattern="CmRdPd", loop=None, width=48, vocab=90, taps=1, rec_heads=2, rec_key_heads=2),
+    # no attention layer at all (no pages are ever read), the whole stack looped, a width and head sizes that are multiples of two only
+    "recurrent": dict(pattern="RdCm", loop=(0, 2, 2), width=54, vocab=91, rec_heads=2, rec_key_heads=1, rec_dim=10, rec_vdim=14, ret_heads=3, ret_dim=6,
+                      ret_vdim=10, ret_rot_dims=4, ff=70, experts=3, identity=1, top=2, expert_ff=18, taps=5),
 }
 _models: dict = {}
 

@@ -195,9 +195,29 @@ delta_scan_kernel(const T *__restrict__ q, long long q_token, long long q_head, 
 // Between the two passes: walk a sequence's segments in order, S_start[c + 1] = P[c] S_start[c] + L[c], and leave every
 // segment's START state where its L was.  One CTA per (sequence, head, 32 state columns): the columns never mix.  The
 // CTA keeps its 32 columns of S in shared memory, lanes = columns; pass 1 stored P transposed (Pt[j][row]), so with the
-// segment's Pt staged in shared memory a warp takes four rows at a time from one 16-byte broadcast read per j; every sum
-// runs over j in order.  STAGE = false (dk too large for shared memory) reads Pt from global memory instead.
+// segment's Pt staged in shared memory (the next segment's arrives by cp.async meanwhile) a warp takes four rows at a time
+// from one 16-byte broadcast read per j; every sum runs over j in order.  STAGE = false (dk too large for shared memory)
+// reads Pt from global memory instead.
 constexpr int kDcThreads = 256;
+
+__device__ __forceinline__ void dr_cp_async16(void *dst, const void *src) {
+    unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
+
+// Pt of one segment into shared memory, rows padded to dkp: 16-byte asynchronous copies when nothing has to be padded, else
+// plain loads; one commit group per call either way.
+__device__ __forceinline__ void dr_stage_pt(float *dst, const float *src, int dk, int dkp) {
+    if (dk == dkp) {
+        for (int e = threadIdx.x * 4; e < dk * dk; e += kDcThreads * 4) dr_cp_async16(dst + e, src + e);
+    } else {
+        for (int e = threadIdx.x; e < dk * dkp; e += kDcThreads) {
+            int j = e / dkp, row = e - j * dkp;
+            dst[e] = row < dk ? src[(size_t)j * dk + row] : 0.f;
+        }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
 
 template <bool STAGE>
 __global__ void __launch_bounds__(kDcThreads)
@@ -205,7 +225,8 @@ delta_combine_kernel(const int32_t *__restrict__ seq_info, const float *__restri
                      int dv, int max_segments, float *__restrict__ seg_state, const float *__restrict__ seg_trans) {
     extern __shared__ float4 combine_smem[];
     const int dkp = (dk + 3) & ~3;                   // rows padded to whole groups of four
-    float *cur = (float *)combine_smem, *nxt = cur + dkp * kDrCols, *pt = nxt + dkp * kDrCols;  // [dkp][32] x 2, then Pt [dk][dkp]
+    float *cur = (float *)combine_smem, *nxt = cur + dkp * kDrCols;  // [dkp][32] each
+    float *pt = nxt + dkp * kDrCols, *pt_next = pt + dk * dkp;        // STAGE: Pt [dk][dkp] of this segment and of the next
     const int colblocks = (dv + kDrCols - 1) / kDrCols;
     const int s = blockIdx.x, head = blockIdx.y / colblocks, col0 = (blockIdx.y % colblocks) * kDrCols;
     const int count = seq_info[s * 4 + 1], start = seq_info[s * 4 + 2], slot = seq_info[s * 4 + 3];
@@ -216,21 +237,24 @@ delta_combine_kernel(const int32_t *__restrict__ seq_info, const float *__restri
     const float *mine = state + (size_t)(slot_ok ? slot : 0) * slot_stride + (size_t)head * dk * dv;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, col = col0 + lane, warps = kDcThreads / 32;
     const bool col_ok = col < dv;
+    const size_t idx0 = (size_t)s * max_segments * heads + head, idx_step = heads;  // workspace index of segment c: idx0 + c * idx_step
+    if (STAGE) dr_stage_pt(pt, seg_trans + idx0 * dk * dk, dk, dkp);
     for (int row = warp; row < dkp; row += warps)
         cur[row * kDrCols + lane] = (row < dk && start > 0 && slot_ok && col_ok) ? mine[(size_t)row * dv + col] : 0.f;
-    __syncthreads();
     for (int c = 0; c < nseg; ++c) {
-        const size_t idx = ((size_t)s * max_segments + c) * heads + head;
+        const size_t idx = idx0 + (size_t)c * idx_step;
         float *cell = seg_state + idx * dk * dv;
         const float *gpt = seg_trans + idx * dk * dk;  // Pt[j * dk + row]
         const bool last = c == nseg - 1;
-        if (STAGE && !last) {
-            for (int e = threadIdx.x; e < dk * dkp; e += kDcThreads) {
-                int j = e / dkp, row = e - j * dkp;
-                pt[e] = row < dk ? gpt[(size_t)j * dk + row] : 0.f;
+        if (STAGE && !last) {  // the next segment's Pt loads under this segment's products
+            if (c + 1 < nseg - 1) {
+                dr_stage_pt(pt_next, seg_trans + (idx + idx_step) * dk * dk, dk, dkp);
+                asm volatile("cp.async.wait_group 1;" ::: "memory");
+            } else {
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
             }
-            __syncthreads();
         }
+        __syncthreads();  // cur (and pt) are complete
         for (int g4 = warp * 4; g4 < dkp; g4 += warps * 4) {
             float local[4], acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -241,6 +265,7 @@ delta_combine_kernel(const int32_t *__restrict__ seq_info, const float *__restri
                 if (ok) cell[(size_t)row * dv + col] = cur[row * kDrCols + lane];  // the segment's start state
             }
             if (last) continue;
+#pragma unroll 4
             for (int j = 0; j < dk; ++j) {
                 const float x = cur[j * kDrCols + lane];
                 if (STAGE) {
@@ -258,10 +283,13 @@ delta_combine_kernel(const int32_t *__restrict__ seq_info, const float *__restri
 #pragma unroll
             for (int i = 0; i < 4; ++i) nxt[(g4 + i) * kDrCols + lane] = acc[i] + local[i];
         }
-        __syncthreads();
+        __syncthreads();  // everybody is done with cur and pt
         float *t = cur;
         cur = nxt;
         nxt = t;
+        t = pt;
+        pt = pt_next;
+        pt_next = t;
     }
 }
 
@@ -269,7 +297,7 @@ delta_combine_kernel(const int32_t *__restrict__ seq_info, const float *__restri
 // K-1 inputs before this step's first token coming from the sequence's slot (hist [C, K-1] fp32, oldest first).  One
 // thread per (channel, token of a chunk); the CTA of a sequence's first chunk also leaves the slot holding the last
 // K-1 inputs for the next step (it is the only one that reads the slot, so nothing races).
-constexpr int kConvMaxTaps = 8;
+constexpr int kConvMaxTaps = 16;
 
 template <typename T>
 __global__ void __launch_bounds__(128)
@@ -380,8 +408,8 @@ int tlb_delta_scan(const void *q, long long q_token, long long q_head, const voi
     TLB_DR(1, colblocks + kblocks, max_segments);
     TL_LAUNCH_CHECK("delta_scan (local states and transitions)");
     const int dkp = (dk + 3) & ~3;
-    const size_t states = (size_t)2 * dkp * kDrCols * sizeof(float), staged = states + (size_t)dk * dkp * sizeof(float);
-    const bool stage = staged <= 160 * 1024;
+    const size_t states = (size_t)2 * dkp * kDrCols * sizeof(float), staged = states + (size_t)2 * dk * dkp * sizeof(float);
+    const bool stage = staged <= 200 * 1024;
     const size_t smem = stage ? staged : states;
     auto combine = stage ? delta_combine_kernel<true> : delta_combine_kernel<false>;
     if (smem > 48 * 1024) {

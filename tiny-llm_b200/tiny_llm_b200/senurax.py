@@ -127,7 +127,7 @@ class SenuraxModel(RaggedDecoderModel):
                 recurrent = self._delta(m["right"], rp, take, channel=False)
                 parts = [(lp + n, take(lp + n), None) for n in ("q", "k", "v")] + [(rp + n, take(rp + n), None) for n in ("q", "k", "v", "g", "a", "b")]
                 outs = (take(lp + "out"), take(rp + "out"))
-            mlp = self._feed_forward(spec.get("mlp"), f"l{i}.mlp.", take)
+            mlp = self._feed_forward(spec.get("mlp"), f"l{i}.mlp.", take, tensors)
             self.layers.append(SenuraxLayer(kind, take(f"l{i}.norm1"), take(f"l{i}.norm2") if mlp is not None else None,
                                             FusedProjection(parts, dtype, self.device), p, mlp, attention, recurrent, outs))
 
@@ -175,7 +175,7 @@ class SenuraxModel(RaggedDecoderModel):
                               gate_act="sigmoid" if channel else "silu")
 
     @staticmethod
-    def _feed_forward(spec, prefix: str, take):
+    def _feed_forward(spec, prefix: str, take, tensors):
         if not spec:
             return None
         if spec["kind"] == "dense":
@@ -184,7 +184,7 @@ class SenuraxModel(RaggedDecoderModel):
             raise ValueError(f"unknown feed-forward kind {spec['kind']!r}")
         r = spec["router"]
         experts, top, identity = int(r["experts"]), int(r["top"]), int(r.get("identity", 0))
-        router = TopKRouter(take(prefix + "router"), None, top, scoring="softmax_all", choice_bias=take(prefix + "correction"),
+        router = TopKRouter(take(prefix + "router"), None, top, scoring="softmax_all", choice_bias=take(prefix + "correction") if prefix + "correction" in tensors else None,
                             weight_scale=float(r.get("scale", 1.0)))
         stack = lambda part: torch.stack([take(f"{prefix}e{k}.{part}") for k in range(experts)]).contiguous()
         return MixtureOfExperts(router, stack("gate"), stack("up"), stack("down"), "silu", identity=identity)
