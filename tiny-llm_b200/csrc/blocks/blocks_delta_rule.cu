@@ -294,49 +294,103 @@ delta_combine_kernel(const int32_t *__restrict__ seq_info, const float *__restri
 }
 
 // y[t, c] = silu(sum_i taps[c, K-1-i] * x[t - i, c]) along each sequence, inputs before position 0 being zero and the
-// K-1 inputs before this step's first token coming from the sequence's slot (hist [C, K-1] fp32, oldest first).  One
-// thread per (channel, token of a chunk); the CTA of a sequence's first chunk also leaves the slot holding the last
-// K-1 inputs for the next step (it is the only one that reads the slot, so nothing races).
+// K-1 inputs before this step's first token coming from the sequence's slot (hist [C, K-1] fp32, oldest first).  A thread
+// owns V adjacent channels (V = 2: one 4- or 8-byte access per token) for a chunk of tokens and slides the last K inputs
+// through registers, so every input is read once (plus the K-1 before the chunk).  KT = the number of taps when it is one
+// of the usual few (the window then lives in registers with no moves), 0 = any number up to kConvMaxTaps.  The CTAs of a
+// sequence's first chunk also leave the slot holding the last K-1 inputs for the next step (they are the only ones that
+// read the slot, and a thread reads what it needs of its channels before it writes them, so nothing races).
 constexpr int kConvMaxTaps = 16;
+constexpr int kConvChunk = 64;
 
-template <typename T>
-__global__ void __launch_bounds__(128)
-short_conv_kernel(const T *__restrict__ x, long long x_token, const T *__restrict__ taps, int channels, int K, int act,
-                  const int32_t *__restrict__ seq_info, float *__restrict__ state, long long slot_stride, int num_slots, T *__restrict__ y,
-                  int chunk) {
-    const int s = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
-    const int first = seq_info[s * 4 + 0], count = seq_info[s * 4 + 1], start = seq_info[s * 4 + 2], slot = seq_info[s * 4 + 3];
-    const int lo = blockIdx.z * chunk, hi = min(count, lo + chunk);
-    if (c >= channels || lo >= count) return;
-    const bool slot_ok = slot >= 0 && slot < num_slots;
-    float *hist = state + (size_t)(slot_ok ? slot : 0) * slot_stride + (size_t)c * (K - 1);
-    float w[kConvMaxTaps], old[kConvMaxTaps];
-#pragma unroll
-    for (int i = 0; i < kConvMaxTaps; ++i) {
-        w[i] = i < K ? to_f(taps[(size_t)c * K + (K - 1 - i)]) : 0.f;  // w[i] multiplies the input i tokens back
-        // old[i] = the input i + 1 tokens before this step's first token
-        old[i] = (blockIdx.z == 0 && i < K - 1 && slot_ok && start - 1 - i >= 0) ? hist[K - 2 - i] : 0.f;
+template <typename T, int V> struct ConvIo;
+template <typename T> struct ConvIo<T, 1> {
+    static __device__ __forceinline__ void load(const T *p, float *v) { v[0] = to_f(p[0]); }
+    static __device__ __forceinline__ void store(T *p, const float *v) { p[0] = from_f<T>(v[0]); }
+};
+template <> struct ConvIo<float, 2> {
+    static __device__ __forceinline__ void load(const float *p, float *v) { float2 t = *reinterpret_cast<const float2 *>(p); v[0] = t.x, v[1] = t.y; }
+    static __device__ __forceinline__ void store(float *p, const float *v) { *reinterpret_cast<float2 *>(p) = make_float2(v[0], v[1]); }
+};
+template <> struct ConvIo<bf16, 2> {
+    static __device__ __forceinline__ void load(const bf16 *p, float *v) {
+        float2 t = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(p));
+        v[0] = t.x, v[1] = t.y;
     }
-    for (int j = lo; j < hi; ++j) {
-        float acc = 0.f;
+    static __device__ __forceinline__ void store(bf16 *p, const float *v) { *reinterpret_cast<__nv_bfloat162 *>(p) = __floats2bfloat162_rn(v[0], v[1]); }
+};
+
+template <typename T, int V, int KT>
+__global__ void __launch_bounds__(128)
+short_conv_kernel(const T *__restrict__ x, long long x_token, const T *__restrict__ taps, int channels, int num_taps, int act,
+                  const int32_t *__restrict__ seq_info, float *__restrict__ state, long long slot_stride, int num_slots, T *__restrict__ y) {
+    constexpr int KM = KT ? KT : kConvMaxTaps;
+    const int K = KT ? KT : num_taps;
+    const int s = blockIdx.x, c = (blockIdx.y * blockDim.x + threadIdx.x) * V;
+    const int first = seq_info[s * 4 + 0], count = seq_info[s * 4 + 1], start = seq_info[s * 4 + 2], slot = seq_info[s * 4 + 3];
+    const int lo = blockIdx.z * kConvChunk, hi = min(count, lo + kConvChunk);
+    if (c >= channels || lo >= count) return;
+    const bool head_chunk = blockIdx.z == 0, slot_ok = slot >= 0 && slot < num_slots;
+    float *hist = state + (size_t)(slot_ok ? slot : 0) * slot_stride + (size_t)c * (K - 1);  // channel c + v: hist + v * (K - 1)
+    float w[V][KM], win[V][KM], old[V][KM];  // w[i] multiplies the input i tokens back = win[i]; old[i] = the input i + 1 tokens before the step
 #pragma unroll
-        for (int i = 0; i < kConvMaxTaps; ++i) {
-            if (i < K) {
-                int jj = j - i;
-                float in = jj >= 0 ? to_f(x[(size_t)(first + jj) * x_token + c]) : old[min(-jj - 1, kConvMaxTaps - 1)];
-                acc = fmaf(w[i], in, acc);
+    for (int v = 0; v < V; ++v)
+#pragma unroll
+        for (int i = 0; i < KM; ++i) {
+            w[v][i] = i < K ? to_f(taps[(size_t)(c + v) * K + (K - 1 - i)]) : 0.f;
+            old[v][i] = (head_chunk && i < K - 1 && slot_ok && start - 1 - i >= 0) ? hist[v * (K - 1) + K - 2 - i] : 0.f;
+            win[v][i] = 0.f;
+        }
+    float in[V];
+#pragma unroll
+    for (int i = 1; i < KM; ++i) {
+        if (i < K) {
+            if (head_chunk) {
+#pragma unroll
+                for (int v = 0; v < V; ++v) win[v][i] = old[v][i - 1];
+            } else {  // lo >= kConvChunk > K: the inputs before the chunk are this step's
+                ConvIo<T, V>::load(x + (size_t)(first + lo - i) * x_token + c, in);
+#pragma unroll
+                for (int v = 0; v < V; ++v) win[v][i] = in[v];
             }
         }
-        if (act == 1) acc = acc / (1.0f + expf(-acc));
-        y[(size_t)(first + j) * channels + c] = from_f<T>(acc);
     }
-    if (blockIdx.z == 0 && slot_ok) {
-        // hist[m] <- the input K-1-m tokens before the NEXT step's first token, m = 0 .. K-2
+    for (int j = lo; j < hi; ++j) {
+        ConvIo<T, V>::load(x + (size_t)(first + j) * x_token + c, in);
+        float out[V];
 #pragma unroll
-        for (int i = 0; i < kConvMaxTaps; ++i) {
+        for (int v = 0; v < V; ++v) {
+            win[v][0] = in[v];
+            float acc = 0.f;
+#pragma unroll
+            for (int i = 0; i < KM; ++i)
+                if (i < K) acc = fmaf(w[v][i], win[v][i], acc);
+            out[v] = act == 1 ? acc / (1.0f + expf(-acc)) : acc;
+#pragma unroll
+            for (int i = KM - 1; i > 0; --i) win[v][i] = win[v][i - 1];
+        }
+        ConvIo<T, V>::store(y + (size_t)(first + j) * channels + c, out);
+    }
+    if (head_chunk && slot_ok) {
+        // hist[K-2-i] <- the input i tokens before the step's last one, i = 0 .. K-2: of this step, or (a step shorter than
+        // K-1 tokens) what the slot held, i - count places further back
+#pragma unroll
+        for (int i = 0; i < KM - 1; ++i) {
             if (i < K - 1) {
-                int jj = count - 1 - i;  // i tokens before the last one of this step
-                hist[K - 2 - i] = jj >= 0 ? to_f(x[(size_t)(first + jj) * x_token + c]) : old[min(-jj - 1, kConvMaxTaps - 1)];
+                const int jj = count - 1 - i;
+                if (jj >= 0) {
+                    ConvIo<T, V>::load(x + (size_t)(first + jj) * x_token + c, in);
+                } else {
+#pragma unroll
+                    for (int v = 0; v < V; ++v) {
+                        in[v] = 0.f;
+#pragma unroll
+                        for (int m = 0; m < KM - 1; ++m)
+                            if (m == -jj - 1) in[v] = old[v][m];
+                    }
+                }
+#pragma unroll
+                for (int v = 0; v < V; ++v) hist[v * (K - 1) + K - 2 - i] = in[v];
             }
         }
     }
@@ -433,11 +487,26 @@ int tlb_short_conv(const void *x, long long x_token, const void *taps, int chann
         act < 0 || act > 1)
         return tl::fail(TL_EINVAL, "short_conv: bad argument");
     if (num_taps > kConvMaxTaps) return tl::fail(TL_EINVAL, "short_conv: %d taps > %d", num_taps, kConvMaxTaps);
-    const int chunk = 32;
-    dim3 grid(num_seqs, ceil_div(channels, 128), ceil_div(max_tokens_per_seq, chunk));
-    TLB_DISPATCH(dtype, "short_conv",
-                 short_conv_kernel<T><<<grid, 128, 0, as_stream(stream)>>>((const T *)x, x_token, (const T *)taps, channels, num_taps, act, seq_info,
-                                                                          state, slot_stride, num_slots, (T *)y, chunk));
+    static_assert(kConvChunk >= kConvMaxTaps, "a chunk after the first finds its K-1 earlier inputs in this step");
+    const size_t esize = dtype == TL_F32 ? 4 : 2;
+    // two channels per thread when every pair sits on a 2-element boundary
+    const bool pairs = channels % 2 == 0 && x_token % 2 == 0 && (uintptr_t)x % (2 * esize) == 0 && (uintptr_t)y % (2 * esize) == 0;
+    const int per = pairs ? 2 : 1;
+    dim3 grid(num_seqs, ceil_div(ceil_div(channels, per), 128), ceil_div(max_tokens_per_seq, kConvChunk));
+    cudaStream_t st = as_stream(stream);
+#define TLB_SC(V, KT)                                                                                                                    \
+    short_conv_kernel<T, V, KT><<<grid, 128, 0, st>>>((const T *)x, x_token, (const T *)taps, channels, num_taps, act, seq_info, state, slot_stride, \
+                                                      num_slots, (T *)y)
+#define TLB_SC_K(V)                                                                                                                      \
+    switch (num_taps) {                                                                                                                  \
+        case 2: TLB_SC(V, 2); break;                                                                                                     \
+        case 3: TLB_SC(V, 3); break;                                                                                                     \
+        case 4: TLB_SC(V, 4); break;                                                                                                     \
+        default: TLB_SC(V, 0);                                                                                                           \
+    }
+    TLB_DISPATCH(dtype, "short_conv", if (pairs) { TLB_SC_K(2) } else { TLB_SC_K(1) });
+#undef TLB_SC_K
+#undef TLB_SC
     TL_LAUNCH_CHECK("short_conv");
     return TL_OK;
 }
