@@ -1199,10 +1199,10 @@ SENURAX_SIZES = {
     # are entered through the loop's mixing product (one pass).  The Bapovik arm (the framework's closest model: fp32 stream,
     # attention beside a recurrent mixer with state slots, experts, the same ragged step) has the same width, depth, head counts,
     # head sizes and expert count; its ungated experts have 3/2 of the width, so that an expert has the same number of weights.
-    "w1024": dict(width=1024, vocab=32768, pattern="RdCmPmPm", loop=(1, 3, 1), heads=8, kv_heads=2, dim=96, vdim=64, rot_dims=48, rot_factor=4.0,
+    "w1024": dict(width=1024, vocab=32768, pattern="RdCmPmPm", loop=(1, 3, 1), heads=8, kv_heads=2, dim=96, vdim=64, rot_dims=64, rot_factor=8.0,
                   rec_heads=8, rec_key_heads=4, rec_dim=64, rec_vdim=128, taps=4, ret_heads=8, ret_dim=64, ret_vdim=128, ret_rot_dims=64, ff=1536,
                   experts=16, identity=2, top=2, expert_ff=512),
-    "w2048": dict(width=2048, vocab=32768, pattern="RdCmPmPm", loop=(1, 3, 1), heads=16, kv_heads=4, dim=192, vdim=128, rot_dims=96, rot_factor=4.0,
+    "w2048": dict(width=2048, vocab=32768, pattern="RdCmPmPm", loop=(1, 3, 1), heads=16, kv_heads=4, dim=192, vdim=128, rot_dims=128, rot_factor=8.0,
                   rec_heads=16, rec_key_heads=8, rec_dim=64, rec_vdim=128, taps=4, ret_heads=16, ret_dim=64, ret_vdim=128, ret_rot_dims=64, ff=8192,
                   experts=64, identity=4, top=6, expert_ff=1408),
 }
@@ -1272,8 +1272,8 @@ def _senurax_kernels(cfg: dict, device, prompt: int, batch: int, context: int) -
         q, k = (torch.randn((T, RH, rk), device=device).to(bf) for _ in range(2))
         v = torch.randn((T, RH, rv), device=device).to(bf)
         pos = torch.cat([torch.arange(start, start + tokens_per_seq, dtype=torch.int32) for _ in range(seqs)]).to(device)
-        tables = blocks.rope_table(pos, dims=rot, base=1e6)
-        decay = torch.linspace(0.97, 0.9995, RH, device=device)
+        tables = blocks.rope_table(pos, dims=rot, base=1e5)
+        decay = torch.linspace(0.9, 0.999, RH, device=device)
         info = torch.tensor([(s * tokens_per_seq, tokens_per_seq, start, s) for s in range(seqs)], dtype=torch.int32, device=device)
         state = torch.zeros((seqs, RH, rk, rv), device=device)
         return timed(lambda: blocks.decay_scan(q, k, v, None, None, q_scale=rk ** -0.5, seq_info=info, state=state, max_tokens=tokens_per_seq, head_decay=decay,
@@ -1310,7 +1310,7 @@ def _senurax_kernels(cfg: dict, device, prompt: int, batch: int, context: int) -
     out["causal_attention_decode"] = stream(batch * context * AG * (ak + av) * 2, ms, kernel=kernel, batch=batch, context=context)
     x = torch.randn((big, AH * ak), device=device).to(bf)
     pos = torch.arange(big, dtype=torch.int32, device=device)
-    ms = timed(lambda: blocks.rope_rows(x, pos, heads=AH, head_stride=ak, first=0, dims=cfg["rot_dims"], base=5e5, interleaved=True, factor=cfg["rot_factor"]))
+    ms = timed(lambda: blocks.rope_rows(x, pos, heads=AH, head_stride=ak, first=0, dims=cfg["rot_dims"], base=1e4, interleaved=True, factor=cfg["rot_factor"]))
     out["rope_rows"] = stream(big * AH * cfg["rot_dims"] * 2 * 2, ms, rows=big)
 
     D, E, ident, top, ff = cfg["width"], cfg["experts"], cfg["identity"], cfg["top"], cfg["expert_ff"]
