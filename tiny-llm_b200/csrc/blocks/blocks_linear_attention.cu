@@ -1,8 +1,11 @@
-// Linear attention with a per-channel decay (a recurrent mixer) over ragged batches, its state kept in fp32 slots.
+// Linear attention with a decay (a recurrent mixer) over ragged batches, its state kept in fp32 slots.
 //
 // Per sequence and head a matrix S [dk, dv] is carried from token to token:
 //     S <- diag(alpha_t) S + k_t v_t^T,      o_t = S^T (q_scale * q_t),
 //     alpha_t = sigmoid(z_t + bias)^(1 / tau) = exp(log_sigmoid(z_t + bias) / tau)        (per key channel)
+// or, given head_decay, one fixed alpha per head (retention).  With rotation tables the first rope_dims entries of every
+// head of q and k are rotated by the token's tabulated angle while they are staged, in fp32: what enters the recurrence is
+// never rounded back to the projections' type.
 // The columns of S never mix, so a CTA owns 32 of them for one (sequence, head) and walks tokens in order; 4 lanes share
 // a column, each holding every 4th row of it in registers.  The tokens' q, k and decays are staged 16 (8 for dk > 128) at a time in shared
 // memory as fp32 (the decay is computed there, in fp32, from the fp32 logits).  A sequence that starts at position 0
