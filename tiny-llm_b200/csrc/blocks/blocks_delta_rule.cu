@@ -296,12 +296,12 @@ delta_combine_kernel(const int32_t *__restrict__ seq_info, const float *__restri
 // y[t, c] = silu(sum_i taps[c, K-1-i] * x[t - i, c]) along each sequence, inputs before position 0 being zero and the
 // K-1 inputs before this step's first token coming from the sequence's slot (hist [C, K-1] fp32, oldest first).  A thread
 // owns V adjacent channels (V = 2: one 4- or 8-byte access per token) for a chunk of tokens and slides the last K inputs
-// through registers, so every input is read once (plus the K-1 before the chunk).  KT = the number of taps when it is one
+// through registers, so every input is read once (plus the K-1 before the chunk), eight tokens' inputs fetched ahead.  KT = the number of taps when it is one
 // of the usual few (the window then lives in registers with no moves), 0 = any number up to kConvMaxTaps.  The CTAs of a
 // sequence's first chunk also leave the slot holding the last K-1 inputs for the next step (they are the only ones that
 // read the slot, and a thread reads what it needs of its channels before it writes them, so nothing races).
 constexpr int kConvMaxTaps = 16;
-constexpr int kConvChunk = 64;
+constexpr int kConvChunk = 64, kConvSmallChunk = 16;  // tokens per CTA; the small one when the launch would leave SMs idle
 
 template <typename T, int V> struct ConvIo;
 template <typename T> struct ConvIo<T, 1> {
@@ -320,7 +320,7 @@ template <> struct ConvIo<bf16, 2> {
     static __device__ __forceinline__ void store(bf16 *p, const float *v) { *reinterpret_cast<__nv_bfloat162 *>(p) = __floats2bfloat162_rn(v[0], v[1]); }
 };
 
-template <typename T, int V, int KT>
+template <typename T, int V, int KT, int CH /* tokens per CTA */>
 __global__ void __launch_bounds__(128)
 short_conv_kernel(const T *__restrict__ x, long long x_token, const T *__restrict__ taps, int channels, int num_taps, int act,
                   const int32_t *__restrict__ seq_info, float *__restrict__ state, long long slot_stride, int num_slots, T *__restrict__ y) {
@@ -328,7 +328,7 @@ short_conv_kernel(const T *__restrict__ x, long long x_token, const T *__restric
     const int K = KT ? KT : num_taps;
     const int s = blockIdx.x, c = (blockIdx.y * blockDim.x + threadIdx.x) * V;
     const int first = seq_info[s * 4 + 0], count = seq_info[s * 4 + 1], start = seq_info[s * 4 + 2], slot = seq_info[s * 4 + 3];
-    const int lo = blockIdx.z * kConvChunk, hi = min(count, lo + kConvChunk);
+    const int lo = blockIdx.z * CH, hi = min(count, lo + CH);
     if (c >= channels || lo >= count) return;
     const bool head_chunk = blockIdx.z == 0, slot_ok = slot >= 0 && slot < num_slots;
     float *hist = state + (size_t)(slot_ok ? slot : 0) * slot_stride + (size_t)c * (K - 1);  // channel c + v: hist + v * (K - 1)
@@ -348,28 +348,37 @@ short_conv_kernel(const T *__restrict__ x, long long x_token, const T *__restric
             if (head_chunk) {
 #pragma unroll
                 for (int v = 0; v < V; ++v) win[v][i] = old[v][i - 1];
-            } else {  // lo >= kConvChunk > K: the inputs before the chunk are this step's
+            } else {  // lo >= CH >= K: the inputs before the chunk are this step's
                 ConvIo<T, V>::load(x + (size_t)(first + lo - i) * x_token + c, in);
 #pragma unroll
                 for (int v = 0; v < V; ++v) win[v][i] = in[v];
             }
         }
     }
-    for (int j = lo; j < hi; ++j) {
-        ConvIo<T, V>::load(x + (size_t)(first + j) * x_token + c, in);
-        float out[V];
+    constexpr int kAhead = 8;  // inputs fetched before any of them is used: the loads of a thread overlap
+    for (int j0 = lo; j0 < hi; j0 += kAhead) {
+        float ahead[kAhead][V];
 #pragma unroll
-        for (int v = 0; v < V; ++v) {
-            win[v][0] = in[v];
-            float acc = 0.f;
+        for (int u = 0; u < kAhead; ++u)
+            if (j0 + u < hi) ConvIo<T, V>::load(x + (size_t)(first + j0 + u) * x_token + c, ahead[u]);
 #pragma unroll
-            for (int i = 0; i < KM; ++i)
-                if (i < K) acc = fmaf(w[v][i], win[v][i], acc);
-            out[v] = act == 1 ? acc / (1.0f + expf(-acc)) : acc;
+        for (int u = 0; u < kAhead; ++u) {
+            if (j0 + u < hi) {
+                float out[V];
 #pragma unroll
-            for (int i = KM - 1; i > 0; --i) win[v][i] = win[v][i - 1];
+                for (int v = 0; v < V; ++v) {
+                    win[v][0] = ahead[u][v];
+                    float acc = 0.f;
+#pragma unroll
+                    for (int i = 0; i < KM; ++i)
+                        if (i < K) acc = fmaf(w[v][i], win[v][i], acc);
+                    out[v] = act == 1 ? acc / (1.0f + expf(-acc)) : acc;
+#pragma unroll
+                    for (int i = KM - 1; i > 0; --i) win[v][i] = win[v][i - 1];
+                }
+                ConvIo<T, V>::store(y + (size_t)(first + j0 + u) * channels + c, out);
+            }
         }
-        ConvIo<T, V>::store(y + (size_t)(first + j) * channels + c, out);
     }
     if (head_chunk && slot_ok) {
         // hist[K-2-i] <- the input i tokens before the step's last one, i = 0 .. K-2: of this step, or (a step shorter than
@@ -487,16 +496,20 @@ int tlb_short_conv(const void *x, long long x_token, const void *taps, int chann
         act < 0 || act > 1)
         return tl::fail(TL_EINVAL, "short_conv: bad argument");
     if (num_taps > kConvMaxTaps) return tl::fail(TL_EINVAL, "short_conv: %d taps > %d", num_taps, kConvMaxTaps);
-    static_assert(kConvChunk >= kConvMaxTaps, "a chunk after the first finds its K-1 earlier inputs in this step");
+    static_assert(kConvSmallChunk >= kConvMaxTaps, "a chunk after the first finds its K-1 earlier inputs in this step");
     const size_t esize = dtype == TL_F32 ? 4 : 2;
     // two channels per thread when every pair sits on a 2-element boundary
     const bool pairs = channels % 2 == 0 && x_token % 2 == 0 && (uintptr_t)x % (2 * esize) == 0 && (uintptr_t)y % (2 * esize) == 0;
     const int per = pairs ? 2 : 1;
-    dim3 grid(num_seqs, ceil_div(ceil_div(channels, per), 128), ceil_div(max_tokens_per_seq, kConvChunk));
+    const int cblocks = ceil_div(ceil_div(channels, per), 128);
+    const int chunk = (long long)num_seqs * cblocks * ceil_div(max_tokens_per_seq, kConvChunk) < 148 * 8 ? kConvSmallChunk : kConvChunk;
+    dim3 grid(num_seqs, cblocks, ceil_div(max_tokens_per_seq, chunk));
     cudaStream_t st = as_stream(stream);
+#define TLB_SC_C(V, KT, CH)                                                                                                              \
+    short_conv_kernel<T, V, KT, CH><<<grid, 128, 0, st>>>((const T *)x, x_token, (const T *)taps, channels, num_taps, act, seq_info, state,      \
+                                                          slot_stride, num_slots, (T *)y)
 #define TLB_SC(V, KT)                                                                                                                    \
-    short_conv_kernel<T, V, KT><<<grid, 128, 0, st>>>((const T *)x, x_token, (const T *)taps, channels, num_taps, act, seq_info, state, slot_stride, \
-                                                      num_slots, (T *)y)
+    if (chunk == kConvChunk) TLB_SC_C(V, KT, kConvChunk); else TLB_SC_C(V, KT, kConvSmallChunk)
 #define TLB_SC_K(V)                                                                                                                      \
     switch (num_taps) {                                                                                                                  \
         case 2: TLB_SC(V, 2); break;                                                                                                     \
@@ -507,6 +520,7 @@ int tlb_short_conv(const void *x, long long x_token, const void *taps, int chann
     TLB_DISPATCH(dtype, "short_conv", if (pairs) { TLB_SC_K(2) } else { TLB_SC_K(1) });
 #undef TLB_SC_K
 #undef TLB_SC
+#undef TLB_SC_C
     TL_LAUNCH_CHECK("short_conv");
     return TL_OK;
 }
