@@ -492,6 +492,55 @@ def test_unequal_requests_in_one_batch_equal_each_alone_and_pages_and_slots_are_
     assert not pool.used_page_ids and not states.used_slots
 
 
+@pytest.mark.parametrize("seed", range(12))
+def test_random_stacks_and_sizes_in_random_schedules(dev, seed):
+    """Layer order, loop, head counts and groups, head sizes, taps, rotated entries, experts / identity experts / top and the
+    schedule all drawn at random (float32): one request whole and in random portions, three requests interleaved."""
+    import random
+
+    rng = random.Random(seed)
+    n = rng.randint(1, 5)
+    pattern = "".join(rng.choice("RCP") + rng.choice("dmn") for _ in range(n))
+    loop = None
+    if rng.random() < 0.7:
+        a = rng.randint(0, n - 1)
+        loop = (a, rng.randint(a + 1, n), rng.randint(1, 3))
+    group, kv, dim = rng.choice([1, 2, 3]), rng.choice([1, 2]), rng.choice([8, 12, 16, 20, 24, 40])
+    rec_group, rec_keys, experts, identity = rng.choice([1, 2, 4]), rng.choice([1, 2, 3]), rng.randint(1, 7), rng.randint(0, 3)
+    ret_dim = rng.choice([6, 16, 34])
+    config = senurax_config(pattern=pattern, loop=loop, width=rng.choice([40, 50, 64, 72, 100, 136]), vocab=rng.choice([61, 128, 301]), heads=group * kv,
+                            kv_heads=kv, dim=dim, vdim=rng.choice([8, 20, 24, 48, 72]), rot_dims=rng.choice([0, 2, dim // 4 * 2, dim]),
+                            rot_factor=rng.choice([1.0, 2.5]), rot_base=rng.choice([50.0, 1e4]), rec_heads=rec_group * rec_keys, rec_key_heads=rec_keys,
+                            rec_dim=rng.choice([4, 10, 16, 33, 64]), rec_vdim=rng.choice([6, 16, 32, 40, 70]), taps=rng.randint(1, 5),
+                            ret_heads=rng.randint(1, 4), ret_dim=ret_dim, ret_vdim=rng.choice([10, 32, 36]), ret_rot_dims=rng.choice([0, 2, ret_dim]),
+                            ff=rng.choice([30, 64, 100]), experts=experts, identity=identity, top=rng.randint(1, experts + identity),
+                            expert_ff=rng.choice([10, 24, 32]), router_scale=rng.choice([1.0, 2.5]), softcap=rng.choice([None, 7.0, 30.0]))
+    tensors = synthetic_senurax(config, seed=seed)
+    model = model_class("Senurax").from_checkpoint(config, tensors, dtype=torch.float32, device=dev, max_tokens=8 * 64, max_requests=3)
+    V, T = config["vocab"], rng.choice([70, 131, 200])
+    prompts = {"a": ids_for(T, V, 1), "b": ids_for(rng.randint(1, 90), V, 2), "c": ids_for(rng.randint(2, 140), V, 3)}
+    want = {r: O.forward(p, tensors, config) for r, p in prompts.items()}
+    assert row_error(run_schedule(model, {"a": prompts["a"]}, [[("a", T)]])["a"], want["a"]) < 1e-4
+    sizes = []
+    while sum(sizes) < T:
+        sizes.append(min(rng.choice([1, 2, 3, 17, 64, 65, 90]), T - sum(sizes)))
+    assert row_error(run_schedule(model, {"a": prompts["a"]}, [[("a", m)] for m in sizes])["a"], want["a"]) < 1e-4, sizes
+    at, schedule = {r: 0 for r in prompts}, []
+    while any(at[r] < len(prompts[r]) for r in prompts):
+        step = []
+        for r in prompts:
+            left = len(prompts[r]) - at[r]
+            if left and rng.random() < 0.8:
+                step.append((r, min(left, rng.choice([1, 1, 2, 5, 40, 70]))))
+                at[r] += step[-1][1]
+        if step:
+            schedule.append(step)
+    got = run_schedule(model, prompts, schedule)
+    for r in prompts:
+        assert row_error(got[r], want[r]) < 1e-4, (r, schedule)
+    assert not model.page_pool.used_page_ids and not model.state_pool.used_slots
+
+
 def test_long_decoding_keeps_state_and_cache_in_step(dev):
     """600 single-token steps after a two-token prompt (graph replays over growing block tables), against the plain model."""
     model, config, tensors = model_and_oracle(dev, "flat", torch.float32)
