@@ -84,7 +84,10 @@ int tlb_latent_prepare(const void *down, long long down_stride, const void *norm
 int tlb_latent_attention(const void *q_lat, long long ql_token, long long ql_head, const void *q_rot, long long qr_token,
                          long long qr_head, const void *slab, int num_pages, int page_size, int rank, int rot,
                          const int32_t *block_table, int max_pages, const int32_t *tiles, int num_tiles, const int32_t *tok_pos,
-                         int heads, int window, float scale, void *out, long long o_token, long long o_head, int dtype, void *stream);
+                         int heads, int window, float scale, void *out, long long o_token, long long o_head, const float *sink, int dtype,
+                         void *stream);
+/* sink [heads] fp32 (or NULL): one more term exp(sink[h]) in head h's softmax denominator, without a key or a value and
+ * not scaled. */
 
 /* The same on the tensor cores, for the bf16 cache: 32 query rows per CTA = tile_tokens consecutive tokens x min(heads, 32)
  * heads, with tile_tokens = tlb_latent_attention_mma_tile_tokens(heads) the most tokens a tile may hold.  Needs
@@ -95,7 +98,7 @@ int tlb_latent_attention_mma(const void *q_lat, long long ql_token, long long ql
                              long long qr_head, const void *slab, int num_pages, int page_size, int rank, int rot,
                              const int32_t *block_table, int max_pages, const int32_t *tiles, int num_tiles, const int32_t *tok_pos,
                              int heads, int window, float scale, void *out, long long o_token, long long o_head, int splits,
-                             void *workspace, size_t workspace_bytes, void *stream);
+                             void *workspace, size_t workspace_bytes, const float *sink, void *stream);
 /* splits > 1 cuts every tile's key range over that many CTAs (flash decoding: few query rows, long contexts) and a second
  * launch merges the partial sums; workspace: tlb_latent_attention_mma_workspace(...) bytes, no initialisation needed. */
 size_t tlb_latent_attention_mma_workspace(int num_tiles, int heads, int rank, int splits);
@@ -110,7 +113,10 @@ int tlb_paged_attention_tile_tokens(int heads, int kv_heads);
 int tlb_paged_attention(const void *q, long long q_token, long long q_head, const void *slab, int num_pages, int page_size, int dk, int dv,
                         int heads, int kv_heads, const int32_t *block_table, int max_pages, const int32_t *tiles, int num_tiles,
                         const int32_t *tok_pos, int mask, int mask_size, float scale, float softcap, int sink, const void *gate,
-                        long long g_token, void *out, long long o_token, long long o_head, int dtype, void *stream);
+                        long long g_token, void *out, long long o_token, long long o_head, const float *head_bias, int weights, int dtype,
+                        void *stream);
+/* head_bias [heads] fp32 (or NULL): with sink != 0 the sink's term is exp(head_bias[h]) instead of exp(0).  weights 1: no
+ * softmax, a visible key weighs sigmoid(score + head_bias[h]) and nothing is normalised over the keys (no sink, no cap). */
 /* The same on the tensor cores, for the bf16 cache: 32 query rows per CTA = tile_tokens consecutive tokens x the query heads
  * of one key/value head (up to 32), tile_tokens = tlb_paged_attention_mma_tile_tokens(heads, kv_heads) the most tokens a tile
  * may hold.  Needs dk, dv multiples of 8 up to 256 and page_size % 32 == 0 (tlb_paged_attention_mma_supported). */
@@ -120,7 +126,7 @@ int tlb_paged_attention_mma(const void *q, long long q_token, long long q_head, 
                             int heads, int kv_heads, const int32_t *block_table, int max_pages, const int32_t *tiles, int num_tiles,
                             const int32_t *tok_pos, int mask, int mask_size, float scale, float softcap, int sink, const void *gate,
                             long long g_token, void *out, long long o_token, long long o_head, int splits, void *workspace,
-                            size_t workspace_bytes, void *stream);
+                            size_t workspace_bytes, const float *head_bias, int weights, void *stream);
 /* splits > 1 cuts every tile's key range over that many CTAs (few query rows, long key ranges) and a second launch merges the
  * partial sums; workspace: tlb_paged_attention_mma_workspace(...) bytes, no initialisation needed. */
 size_t tlb_paged_attention_mma_workspace(int num_tiles, int heads, int kv_heads, int dv, int splits);
@@ -150,11 +156,20 @@ int tlb_decay_scan(const void *q, long long q_token, long long q_head, const voi
                    long long v_token, long long v_head, const float *z, long long z_token, const void *z_bias, float tau, const float *head_decay,
                    const float *rope_cos, const float *rope_sin, int rope_dims, int rope_interleaved, float q_scale, int heads,
                    int dk, int dv, const int32_t *seq_info, int num_seqs, int max_tokens_per_seq, float *state, long long slot_stride,
-                   int num_slots, float *out, void *workspace, size_t workspace_bytes, int dtype, void *stream);
+                   int num_slots, float *out, void *workspace, size_t workspace_bytes, int decay_kind, const void *a_log, const void *bonus,
+                   int qk_heads, const void *skip, int dtype, void *stream);
+/* decay_kind 0: as above.  2: alpha = exp(-exp(z + z_bias)) per key channel.  3: one decay per head and token,
+ * alpha = exp(-exp(a_log[h]) dt), dt = softplus(z[t, h] + z_bias[h]) (z [T, heads]), and the token's key is multiplied by dt
+ * (a discretised state-space step; a_log [heads] in `dtype`).  qk_heads (0 = heads): q and k have that many heads, head h
+ * reads h / (heads / qk_heads).  skip [heads] (`dtype`, or NULL): out += skip[h] v.  bonus [heads, dk] (`dtype`, or NULL): the
+ * read-out comes before the update and weighs the token's own k v^T by it, out = (S + diag(bonus) k v^T)^T q, then S is
+ * updated. */
 /* out[t, h, :] = o[t, h, :] / rms(o[t, h, :]) * w * act(gate[t, h, :]) (w NULL = no weight; gate rows g_token apart, NULL = no
- * gate; act 0 = the gate as it is, 1 = silu, 2 = sigmoid); o fp32 [tokens, heads, dv], out `dtype` [tokens, heads * dv]. */
+ * gate; act 0 = the gate as it is, 1 = silu, 2 = sigmoid); o fp32 [tokens, heads, dv], out `dtype` [tokens, heads * dv].
+ * wide_weight: w is [heads * dv], each head its own part, instead of [dv]; gate_first: the gate multiplies o BEFORE the
+ * norm, out = n / rms(n) * w with n = o * act(gate). */
 int tlb_head_norm_gate(const float *o, const void *w, float eps, const void *gate, long long g_token, int act, void *out, int tokens, int heads,
-                       int dv, int dtype, void *stream);
+                       int dv, int wide_weight, int gate_first, int dtype, void *stream);
 
 /* Gated delta rule, state in fp32 slots.  Per sequence and head S [dk, dv], token by token:
  *   S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T;  out = S^T q
@@ -174,14 +189,14 @@ int tlb_delta_scan(const void *q, long long q_token, long long q_head, const voi
                    int per_channel, const void *a_log, const void *dt_bias, float q_scale, float unit_eps, int heads, int key_heads, int dk, int dv,
                    const int32_t *seq_info, int num_seqs, int max_tokens_per_seq, float *state, long long slot_stride, int num_slots, float *out,
                    void *workspace, size_t workspace_bytes, int dtype, void *stream);
-/* Short causal convolution along every sequence, per channel: y[t, c] = act(sum_i taps[c, K-1-i] x[t-i, c]) (act 1 = silu,
- * 0 = none), zeros before position 0.  x [T, channels] rows x_token apart, taps [channels, K] (K <= 16), y [T, channels]
+/* Short causal convolution along every sequence, per channel: y[t, c] = act(bias[c] + sum_i taps[c, K-1-i] x[t-i, c]) (act 1 =
+ * silu, 0 = none; bias NULL = none; add_input: x[t, c] is added before the activation), zeros before position 0.  x [T, channels] rows x_token apart, taps [channels, K] (K <= 16), y [T, channels]
  * contiguous.  The K-1 inputs before a step's first token live in the sequence's state slot (state + slot * slot_stride
  * floats, [channels, K-1], oldest first) and are replaced by the step's last ones. */
-int tlb_short_conv(const void *x, long long x_token, const void *taps, int channels, int num_taps, int act, const int32_t *seq_info, int num_seqs,
-                   int max_tokens_per_seq, float *state, long long slot_stride, int num_slots, void *y, int dtype, void *stream);
+int tlb_short_conv(const void *x, long long x_token, const void *taps, const void *bias, int add_input, int channels, int num_taps, int act,
+                   const int32_t *seq_info, int num_seqs, int max_tokens_per_seq, float *state, long long slot_stride, int num_slots, void *y, int dtype, void *stream);
 
-/* out = act(x) elementwise over [rows, width]; act 0 = silu, 1 = gelu (tanh form), 2 = squared relu. */
+/* out = act(x) elementwise over [rows, width]; act 0 = silu, 1 = gelu (tanh form), 2 = squared relu, 4 = tanh. */
 int tlb_act_rows(const void *x, void *out, int rows, int width, int act, int dtype, void *stream);
 /* x <- cap * tanh(x / cap), fp32 [rows, width] in place. */
 int tlb_softcap_rows(float *x, int rows, int width, float cap, void *stream);
@@ -189,7 +204,21 @@ int tlb_softcap_rows(float *x, int rows, int width, float cap, void *stream);
 int tlb_cast_rows(const float *src, void *dst, long long dst_stride, int rows, int dim, int dtype, void *stream);
 
 /* out[t, j] = act(gu[t, j]) * gu[t, width + j]; act 0 = silu, 1 = gelu (tanh form). */
-int tlb_gated_act(const void *gu, void *out, int rows, int width, int act, int dtype, void *stream);
+int tlb_gated_act(const void *gu, void *out, int rows, int width, int act, float limit, float slope, int dtype, void *stream);
+/* act 3: g = min(gate, limit), u = clamp(up, -limit, limit), out = g sigmoid(slope g) (u + 1). */
+
+/* n residual streams xs [rows, n, dim] fp32 around a sublayer, n <= 8.  With write_w (mix [n, n] indexed [from, to], then
+ * out [n]; fp32 on the device) and the sublayer's output y [rows, dim] fp32 (+ y_bias [dim] in `dtype`):
+ *     x_t <- sum_s mix[s, t] x_s + out[t] (y + y_bias); the right-hand side reads the streams as they were before the call.
+ * With read_w (in [n], then the norm's one weight g): h = rms_norm(sum_s in[s] x_s) * g, rounded to `dtype`.  x0 [rows, dim]
+ * fp32: every stream starts as that row (the embedding) instead of being read.  Either half may be absent. */
+int tlb_streams_step(float *xs, const float *x0, const float *y, const void *y_bias, const float *write_w, const float *read_w, float eps, void *h,
+                     int rows, int streams, int dim, int dtype, void *stream);
+/* Token shift: out[i, t, :] = h[t] + (h[t-1] - h[t]) * mu[i] for i < parts <= 8 (mu [parts, dim]); h[-1] is zero at position
+ * 0 and the sequence's slot (state + slot * slot_stride, fp32 [dim]) otherwise; the slot then takes the step's last row.
+ * h rows h_token apart; out [parts] blocks out_part elements apart, each [T, dim]. */
+int tlb_shift_mix(const void *h, long long h_token, const void *mu, int parts, int dim, const int32_t *seq_info, int num_seqs, int max_tokens_per_seq,
+                  float *state, long long slot_stride, int num_slots, void *out, long long out_part, int dtype, void *stream);
 
 /* Router: logits = W h + b in fp32 (h, W, b stored in `dtype`; b may be NULL), the `top` largest per token (lower index
  * wins a tie).  scoring 0: weights = softmax over the chosen logits; 1: weights = sigmoid of each chosen logit, not

@@ -293,7 +293,7 @@ delta_combine_kernel(const int32_t *__restrict__ seq_info, const float *__restri
     }
 }
 
-// y[t, c] = silu(sum_i taps[c, K-1-i] * x[t - i, c]) along each sequence, inputs before position 0 being zero and the
+// y[t, c] = act(bias[c] + sum_i taps[c, K-1-i] * x[t - i, c] (+ x[t, c], add_input)) along each sequence, act = silu or none, inputs before position 0 being zero and the
 // K-1 inputs before this step's first token coming from the sequence's slot (hist [C, K-1] fp32, oldest first).  A thread
 // owns V adjacent channels (V = 2: one 4- or 8-byte access per token) for a chunk of tokens and slides the last K inputs
 // through registers, so every input is read once (plus the K-1 before the chunk), eight tokens' inputs fetched ahead.  KT = the number of taps when it is one
@@ -322,8 +322,8 @@ template <> struct ConvIo<bf16, 2> {
 
 template <typename T, int V, int KT, int CH /* tokens per CTA */>
 __global__ void __launch_bounds__(128)
-short_conv_kernel(const T *__restrict__ x, long long x_token, const T *__restrict__ taps, int channels, int num_taps, int act,
-                  const int32_t *__restrict__ seq_info, float *__restrict__ state, long long slot_stride, int num_slots, T *__restrict__ y) {
+short_conv_kernel(const T *__restrict__ x, long long x_token, const T *__restrict__ taps, const T *__restrict__ bias, int add_input, int channels,
+                  int num_taps, int act, const int32_t *__restrict__ seq_info, float *__restrict__ state, long long slot_stride, int num_slots, T *__restrict__ y) {
     constexpr int KM = KT ? KT : kConvMaxTaps;
     const int K = KT ? KT : num_taps;
     const int s = blockIdx.x, c = (blockIdx.y * blockDim.x + threadIdx.x) * V;
@@ -332,6 +332,9 @@ short_conv_kernel(const T *__restrict__ x, long long x_token, const T *__restric
     if (c >= channels || lo >= count) return;
     const bool head_chunk = blockIdx.z == 0, slot_ok = slot >= 0 && slot < num_slots;
     float *hist = state + (size_t)(slot_ok ? slot : 0) * slot_stride + (size_t)c * (K - 1);  // channel c + v: hist + v * (K - 1)
+    float b0[V];
+#pragma unroll
+    for (int v = 0; v < V; ++v) b0[v] = bias ? to_f(bias[c + v]) : 0.f;
     float w[V][KM], win[V][KM], old[V][KM];  // w[i] multiplies the input i tokens back = win[i]; old[i] = the input i + 1 tokens before the step
 #pragma unroll
     for (int v = 0; v < V; ++v)
@@ -368,10 +371,11 @@ short_conv_kernel(const T *__restrict__ x, long long x_token, const T *__restric
 #pragma unroll
                 for (int v = 0; v < V; ++v) {
                     win[v][0] = ahead[u][v];
-                    float acc = 0.f;
+                    float acc = b0[v];
 #pragma unroll
                     for (int i = 0; i < KM; ++i)
                         if (i < K) acc = fmaf(w[v][i], win[v][i], acc);
+                    if (add_input) acc += win[v][0];
                     out[v] = act == 1 ? acc / (1.0f + expf(-acc)) : acc;
 #pragma unroll
                     for (int i = KM - 1; i > 0; --i) win[v][i] = win[v][i - 1];
@@ -489,7 +493,8 @@ int tlb_delta_scan(const void *q, long long q_token, long long q_head, const voi
     return TL_OK;
 }
 
-int tlb_short_conv(const void *x, long long x_token, const void *taps, int channels, int num_taps, int act, const int32_t *seq_info, int num_seqs,
+int tlb_short_conv(const void *x, long long x_token, const void *taps, const void *bias, int add_input, int channels, int num_taps, int act,
+                   const int32_t *seq_info, int num_seqs,
                    int max_tokens_per_seq, float *state, long long slot_stride, int num_slots, void *y, int dtype, void *stream) {
     if (num_seqs <= 0) return TL_OK;
     if (!x || !taps || !seq_info || !y || channels <= 0 || num_taps <= 0 || max_tokens_per_seq <= 0 || (num_taps > 1 && (!state || num_slots <= 0)) ||
@@ -506,7 +511,7 @@ int tlb_short_conv(const void *x, long long x_token, const void *taps, int chann
     dim3 grid(num_seqs, cblocks, ceil_div(max_tokens_per_seq, chunk));
     cudaStream_t st = as_stream(stream);
 #define TLB_SC_C(V, KT, CH)                                                                                                              \
-    short_conv_kernel<T, V, KT, CH><<<grid, 128, 0, st>>>((const T *)x, x_token, (const T *)taps, channels, num_taps, act, seq_info, state,      \
+    short_conv_kernel<T, V, KT, CH><<<grid, 128, 0, st>>>((const T *)x, x_token, (const T *)taps, (const T *)bias, add_input, channels, num_taps, act, seq_info, state, \
                                                           slot_stride, num_slots, (T *)y)
 #define TLB_SC(V, KT)                                                                                                                    \
     if (chunk == kConvChunk) TLB_SC_C(V, KT, kConvChunk); else TLB_SC_C(V, KT, kConvSmallChunk)

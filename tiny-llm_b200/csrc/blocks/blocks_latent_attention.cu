@@ -24,7 +24,7 @@ latent_attention_kernel(const T *__restrict__ q_lat, long long ql_token, long lo
                         long long qr_head, const T *__restrict__ slab, int num_pages, int page_size, int rank, int rot,
                         const int32_t *__restrict__ block_table, int max_pages, const int32_t *__restrict__ tiles,
                         const int32_t *__restrict__ tok_pos, int heads, int window, float scale, T *__restrict__ out, long long o_token,
-                        long long o_head) {
+                        long long o_head, const float *__restrict__ sink /* [heads]: a term exp(sink[h]) more in the denominator, or NULL */) {
     extern __shared__ float smem[];
     const int width = rank + rot;
     const int kstride = width + 1;           // odd or even, +1 breaks the 32-way conflict of lane = key reads when width % 32 == 0
@@ -52,6 +52,10 @@ latent_attention_kernel(const T *__restrict__ q_lat, long long ql_token, long lo
     const int p0 = pos0 + tq0, p1 = pos0 + tq1;  // positions of this warp's two rows
 
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    if (sink) {  // a key without a value whose score is the head's learned number: the maximum starts there, the sum at 1
+        if (live0) m0 = sink[head0 + r0 % kHeadGroup], l0 = 1.f;
+        if (live1) m1 = sink[head0 + r1 % kHeadGroup], l1 = 1.f;
+    }
     float acc0[RL], acc1[RL];
 #pragma unroll
     for (int i = 0; i < RL; ++i) acc0[i] = acc1[i] = 0.f;
@@ -129,7 +133,7 @@ template <typename T, int RL>
 static int launch(const void *q_lat, long long ql_token, long long ql_head, const void *q_rot, long long qr_token, long long qr_head,
                   const void *slab, int num_pages, int page_size, int rank, int rot, const int32_t *block_table, int max_pages,
                   const int32_t *tiles, int num_tiles, const int32_t *tok_pos, int heads, int window, float scale, void *out, long long o_token,
-                  long long o_head, cudaStream_t st) {
+                  long long o_head, const float *sink, cudaStream_t st) {
     int width = rank + rot;
     size_t smem = ((size_t)kRows * width + (size_t)kKeys * (width + 1)) * sizeof(float);
     auto kernel = latent_attention_kernel<T, RL>;
@@ -141,7 +145,7 @@ static int launch(const void *q_lat, long long ql_token, long long ql_head, cons
     dim3 grid(num_tiles, ceil_div(heads, kHeadGroup));
     kernel<<<grid, kWarps * 32, smem, st>>>((const T *)q_lat, ql_token, ql_head, (const T *)q_rot, qr_token, qr_head, (const T *)slab, num_pages,
                                             page_size, rank, rot, block_table, max_pages, tiles, tok_pos, heads, window, scale, (T *)out, o_token,
-                                            o_head);
+                                            o_head, sink);
     return TL_OK;
 }
 
@@ -152,7 +156,8 @@ using namespace tlb;
 extern "C" int tlb_latent_attention(const void *q_lat, long long ql_token, long long ql_head, const void *q_rot, long long qr_token,
                                     long long qr_head, const void *slab, int num_pages, int page_size, int rank, int rot,
                                     const int32_t *block_table, int max_pages, const int32_t *tiles, int num_tiles, const int32_t *tok_pos,
-                                    int heads, int window, float scale, void *out, long long o_token, long long o_head, int dtype, void *stream) {
+                                    int heads, int window, float scale, void *out, long long o_token, long long o_head, const float *sink, int dtype,
+                                    void *stream) {
     if (num_tiles <= 0) return TL_OK;
     if (!q_lat || (!q_rot && rot > 0) || !slab || !block_table || !tiles || !tok_pos || !out || rank <= 0 || rot < 0 || heads <= 0 ||
         max_pages <= 0 || num_pages <= 0)
@@ -164,7 +169,7 @@ extern "C" int tlb_latent_attention(const void *q_lat, long long ql_token, long 
     int rc = TL_OK;
 #define TLB_LA(RLV)                                                                                                                          \
     rc = launch<T, RLV>(q_lat, ql_token, ql_head, q_rot ? q_rot : q_lat, qr_token, qr_head, slab, num_pages, page_size, rank, rot, block_table, \
-                        max_pages, tiles, num_tiles, tok_pos, heads, window, scale, out, o_token, o_head, st)
+                        max_pages, tiles, num_tiles, tok_pos, heads, window, scale, out, o_token, o_head, sink, st)
     TLB_DISPATCH(dtype, "latent_attention", if (rl <= 4) TLB_LA(4); else if (rl <= 8) TLB_LA(8); else if (rl <= 16) TLB_LA(16); else TLB_LA(32));
 #undef TLB_LA
     if (rc != TL_OK) return rc;

@@ -54,7 +54,7 @@ latent_attention_mma_kernel(const bf16 *__restrict__ q_lat, long long ql_token, 
                             const int32_t *__restrict__ block_table, int max_pages, const int32_t *__restrict__ tiles,
                             const int32_t *__restrict__ tok_pos, int heads, int head_group, int window, float scale, bf16 *__restrict__ out,
                             long long o_token, long long o_head, int row_stride /* shared-memory row stride in elements */,
-                            float *__restrict__ part /* split results, or NULL */) {
+                            float *__restrict__ part /* split results, or NULL */, const float *__restrict__ sink /* [heads] or NULL */) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int width = rank + rot;
     bf16 *sq = reinterpret_cast<bf16 *>(smem_raw);                  // [32][row_stride]
@@ -115,6 +115,8 @@ latent_attention_mma_kernel(const bf16 *__restrict__ q_lat, long long ql_token, 
         int r = warp * 4 + (lane >> 3), tq = r / head_group, hh = r % head_group;
         live_row = tq < count && hh < nheads;
         pos_row = pos0 + tq;
+        // a sink: a key without a value whose score is the head's learned number (counted once when the key range is split)
+        if (sink && live_row && blockIdx.z == 0) m_row = sink[head0 + hh], l_row = 1.f;
     }
     const int mt = warp & 1, nt = warp >> 1;          // score block of this warp; nt is also its quarter of the value columns
     float acc[2 * PAIRS][4];
@@ -315,7 +317,7 @@ extern "C" int tlb_latent_attention_mma(const void *q_lat, long long ql_token, l
                                         long long qr_head, const void *slab, int num_pages, int page_size, int rank, int rot,
                                         const int32_t *block_table, int max_pages, const int32_t *tiles, int num_tiles, const int32_t *tok_pos,
                                         int heads, int window, float scale, void *out, long long o_token, long long o_head, int splits,
-                                        void *workspace, size_t workspace_bytes, void *stream) {
+                                        void *workspace, size_t workspace_bytes, const float *sink, void *stream) {
     if (num_tiles <= 0) return TL_OK;
     if (!q_lat || (!q_rot && rot > 0) || !slab || !block_table || !tiles || !tok_pos || !out || heads <= 0 || max_pages <= 0 || num_pages <= 0)
         return tl::fail(TL_EINVAL, "latent_attention_mma: bad argument");
@@ -344,7 +346,7 @@ extern "C" int tlb_latent_attention_mma(const void *q_lat, long long ql_token, l
         }                                                                                                                                   \
         kernel<<<grid, kMWarps * 32, smem, st>>>((const bf16 *)q_lat, ql_token, ql_head, (const bf16 *)(q_rot ? q_rot : q_lat), qr_token,   \
                                                  qr_head, (const bf16 *)slab, num_pages, page_size, rank, rot, block_table, max_pages, tiles, \
-                                                 tok_pos, heads, head_group, window, scale, (bf16 *)out, o_token, o_head, row_stride, part); \
+                                                 tok_pos, heads, head_group, window, scale, (bf16 *)out, o_token, o_head, row_stride, part, sink); \
     } while (0)
     if (pairs == 1) TLB_LAM(1);
     else if (pairs == 2) TLB_LAM(2);

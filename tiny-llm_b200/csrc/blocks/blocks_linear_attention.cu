@@ -44,7 +44,13 @@ __device__ __forceinline__ bool la_segment(int p0, int n, int c, int &lo, int &h
 //      workspace (the last segment of a sequence is skipped: nobody needs its local state).
 //   3  segment c from the start state that decay_combine_kernel left in the workspace: outputs; the last segment writes
 //      the slot.
-template <typename T, int KR /* rows per lane: dk <= 4 * KR */, int kLaTokens /* tokens staged at a time */>
+//
+// decay_kind chooses where the decay comes from: 0 = sigmoid(z + bias)^(1/tau) per key channel, or head_decay; 2 = exp(-exp(z + bias))
+// per key channel; 3 = one number per head and token, exp(-exp(a_log[h]) dt) with dt = softplus(z[t, h] + bias[h]), and the
+// token's key is multiplied by dt (a discretised state-space step).  q and k may have fewer heads than v (qk_heads; head h
+// reads query/key head h / (heads / qk_heads)).  skip [heads]: o_t += skip[h] v_t.  BONUS: the read-out comes BEFORE the
+// update and sees the token's own k v^T weighted by bonus [heads, dk] instead: o_t = (S + diag(bonus) k_t v_t^T)^T q_t.
+template <typename T, int KR /* rows per lane: dk <= 4 * KR */, int kLaTokens /* tokens staged at a time */, bool BONUS>
 __global__ void __launch_bounds__(kLaCols * kLaLanes)
 decay_scan_kernel(const T *__restrict__ q, long long q_token, long long q_head, const T *__restrict__ k, long long k_token, long long k_head,
                   const T *__restrict__ v, long long v_token, long long v_head, const float *__restrict__ z, long long z_token,
@@ -52,7 +58,8 @@ decay_scan_kernel(const T *__restrict__ q, long long q_token, long long q_head, 
                   const float *__restrict__ rope_sin, int rope_dims, int rope_interleaved, float q_scale, int heads, int dk, int dv,
                   const int32_t *__restrict__ seq_info,
                   float *__restrict__ state, long long slot_stride, int num_slots, float *__restrict__ out, int pass, int max_segments,
-                  float *__restrict__ seg_state, float *__restrict__ seg_decay) {
+                  float *__restrict__ seg_state, float *__restrict__ seg_decay, int decay_kind, const T *__restrict__ a_log,
+                  const T *__restrict__ bonus, int qk_heads, const T *__restrict__ skip) {
     __shared__ float4 sx[kLaTokens * 4 * KR];  // per token and key channel: (decay, k, scaled q, -), one 16-byte read per row
     __shared__ float sv[kLaTokens * kLaCols];
     __shared__ float sprod[4 * KR];
@@ -82,16 +89,24 @@ decay_scan_kernel(const T *__restrict__ q, long long q_token, long long q_head, 
     }
     if (pass == 1)
         for (int d = threadIdx.x; d < dk; d += blockDim.x) sprod[d] = 1.f;
+    const int qk_head = head / (heads / qk_heads);
+    const float rate = decay_kind == 3 ? expf(to_f(a_log[head])) : 0.f;
+    const float skipv = skip ? to_f(skip[head]) : 0.f;
     for (int t0 = 0; t0 < count; t0 += kLaTokens) {
         const int n = min(kLaTokens, count - t0);
         __syncthreads();
         for (int e = threadIdx.x; e < n * dk; e += blockDim.x) {
             int j = e / dk, d = e - j * dk;
             size_t tok = (size_t)(first + t0 + j);
-            float alpha;
+            float alpha, kmul = 1.f;
             if (head_decay) alpha = head_decay[head];
-            else alpha = expf(log_sigmoid(z[tok * z_token + (size_t)head * dk + d] + (z_bias ? to_f(z_bias[(size_t)head * dk + d]) : 0.f)) * inv_tau);
-            const T *kp = k + tok * k_token + (size_t)head * k_head, *qp = q + tok * q_token + (size_t)head * q_head;
+            else if (decay_kind == 2) alpha = expf(-expf(z[tok * z_token + (size_t)head * dk + d] + (z_bias ? to_f(z_bias[(size_t)head * dk + d]) : 0.f)));
+            else if (decay_kind == 3) {
+                const float zz = z[tok * z_token + head] + (z_bias ? to_f(z_bias[head]) : 0.f);
+                const float dt = zz > 20.f ? zz : log1pf(expf(zz));
+                alpha = expf(-rate * dt), kmul = dt;
+            } else alpha = expf(log_sigmoid(z[tok * z_token + (size_t)head * dk + d] + (z_bias ? to_f(z_bias[(size_t)head * dk + d]) : 0.f)) * inv_tau);
+            const T *kp = k + tok * k_token + (size_t)qk_head * k_head, *qp = q + tok * q_token + (size_t)qk_head * q_head;
             float kd = to_f(kp[d]), qd = to_f(qp[d]);
             if (d < rope_dims) {  // rotate the pair this entry belongs to, in fp32, by the token's tabulated angle
                 const int half = rope_dims >> 1;
@@ -102,7 +117,8 @@ decay_scan_kernel(const T *__restrict__ q, long long q_token, long long q_head, 
                 kd = kd * c + to_f(kp[other]) * sn;
                 qd = qd * c + to_f(qp[other]) * sn;
             }
-            sx[j * 4 * KR + d] = make_float4(alpha, kd, qd * q_scale, 0.f);
+            kd *= kmul;
+            sx[j * 4 * KR + d] = make_float4(alpha, kd, qd * q_scale, BONUS ? kd * to_f(bonus[(size_t)head * dk + d]) : 0.f);
         }
         for (int e = threadIdx.x; e < n * kLaCols; e += blockDim.x) {
             int j = e / kLaCols, d = e - j * kLaCols;
@@ -125,20 +141,22 @@ decay_scan_kernel(const T *__restrict__ q, long long q_token, long long q_head, 
                 int row = r + kLaLanes * i;
                 if (row < dk) {
                     float4 x = xa[row];
+                    if (BONUS) o0 = fmaf(x.z, fmaf(x.w, vj, S[i]), o0);
                     S[i] = fmaf(x.x, S[i], x.y * vj);
-                    o0 = fmaf(x.z, S[i], o0);
+                    if (!BONUS) o0 = fmaf(x.z, S[i], o0);
                 }
                 if (row + kLaLanes < dk) {
                     float4 x = xa[row + kLaLanes];
+                    if (BONUS) o1 = fmaf(x.z, fmaf(x.w, vj, S[i + 1]), o1);
                     S[i + 1] = fmaf(x.x, S[i + 1], x.y * vj);
-                    o1 = fmaf(x.z, S[i + 1], o1);
+                    if (!BONUS) o1 = fmaf(x.z, S[i + 1], o1);
                 }
             }
             if (pass != 1) {
                 float o = o0 + o1;
                 o += __shfl_xor_sync(0xffffffffu, o, 1);
                 o += __shfl_xor_sync(0xffffffffu, o, 2);
-                if (r == 0 && col_ok) out[((size_t)(first + t0 + j) * heads + head) * dv + col] = o;
+                if (r == 0 && col_ok) out[((size_t)(first + t0 + j) * heads + head) * dv + col] = fmaf(skipv, vj, o);
             }
         }
     }
@@ -183,27 +201,34 @@ decay_combine_kernel(const int32_t *__restrict__ seq_info, const float *__restri
 }
 
 // out[t, h, :] = o[t, h, :] / rms(o[t, h, :]) * w * act(gate[t, h, :]); one warp per (token, head).  act 0 = none, 1 = silu,
-// 2 = sigmoid; w == NULL: no weight.
+// 2 = sigmoid; w == NULL: no weight; wide_weight: w is [heads * dv] (every head its own part) instead of [dv] shared by the
+// heads; gate_first: the gate multiplies o BEFORE the norm, out = n / rms(n) * w with n = o * act(gate).
 template <typename T>
 __global__ void __launch_bounds__(128)
 head_norm_gate_kernel(const float *__restrict__ o, const T *__restrict__ w, float eps, const T *__restrict__ gate, long long g_token, int act,
-                      T *__restrict__ out, long long rows, int heads, int dv) {
+                      T *__restrict__ out, long long rows, int heads, int dv, int wide_weight, int gate_first) {
     long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= rows) return;
     const int lane = threadIdx.x & 31;
     const long long t = row / heads;
     const int head = (int)(row - t * heads);
     const float *src = o + (size_t)row * dv;
+    auto gated = [&](int d) {
+        float gv = to_f(gate[(size_t)t * g_token + (size_t)head * dv + d]);
+        return act == 1 ? gv / (1.0f + expf(-gv)) : act == 2 ? 1.0f / (1.0f + expf(-gv)) : gv;
+    };
+    const bool first = gate && gate_first;
     float ss = 0.f;
-    for (int d = lane; d < dv; d += 32) ss += src[d] * src[d];
+    for (int d = lane; d < dv; d += 32) {
+        float x = first ? src[d] * gated(d) : src[d];
+        ss += x * x;
+    }
     ss = warp_sum(ss);
     float inv = 1.0f / sqrtf(ss / (float)dv + eps);
+    const T *wr = w ? w + (wide_weight ? (size_t)head * dv : 0) : nullptr;
     for (int d = lane; d < dv; d += 32) {
-        float y = src[d] * inv * (w ? to_f(w[d]) : 1.f);
-        if (gate) {
-            float gv = to_f(gate[(size_t)t * g_token + (size_t)head * dv + d]);
-            y *= act == 1 ? gv / (1.0f + expf(-gv)) : act == 2 ? 1.0f / (1.0f + expf(-gv)) : gv;
-        }
+        float y = src[d] * inv * (wr ? to_f(wr[d]) : 1.f);
+        if (gate) y *= gated(d);
         out[(size_t)row * dv + d] = from_f<T>(y);
     }
 }
@@ -224,8 +249,13 @@ int tlb_decay_scan(const void *q, long long q_token, long long q_head, const voi
                    long long v_token, long long v_head, const float *z, long long z_token, const void *z_bias, float tau, const float *head_decay,
                    const float *rope_cos, const float *rope_sin, int rope_dims, int rope_interleaved, float q_scale, int heads,
                    int dk, int dv, const int32_t *seq_info, int num_seqs, int max_tokens_per_seq, float *state, long long slot_stride, int num_slots,
-                   float *out, void *workspace, size_t workspace_bytes, int dtype, void *stream) {
+                   float *out, void *workspace, size_t workspace_bytes, int decay_kind, const void *a_log, const void *bonus, int qk_heads,
+                   const void *skip, int dtype, void *stream) {
     if (num_seqs <= 0) return TL_OK;
+    if (qk_heads <= 0) qk_heads = heads;
+    if ((decay_kind != 0 && decay_kind != 2 && decay_kind != 3) || (decay_kind != 0 && (!z || head_decay)) || (decay_kind == 3 && !a_log) ||
+        heads % qk_heads)
+        return tl::fail(TL_EINVAL, "decay_scan: bad decay kind or head groups");
     if (!q || !k || !v || (!z && !head_decay) || !seq_info || !state || !out || heads <= 0 || dk <= 0 || dv <= 0 || (z && !(tau > 0.f)) ||
         num_slots <= 0 || max_tokens_per_seq <= 0)
         return tl::fail(TL_EINVAL, "decay_scan: bad argument");
@@ -245,10 +275,12 @@ int tlb_decay_scan(const void *q, long long q_token, long long q_head, const voi
     const int colblocks = ceil_div(dv, kLaCols);
     cudaStream_t st = as_stream(stream);
     int kr = ceil_div(dk, kLaLanes);
-#define TLB_DS_K(KRV, PASS, GZ)                                                                                                                    \
-    decay_scan_kernel<T, KRV, (KRV > 32 ? 8 : 16)><<<dim3(num_seqs, heads * colblocks, GZ), kLaCols * kLaLanes, 0, st>>>(                                                \
+#define TLB_DS_B(KRV, PASS, GZ, BON)                                                                                                                \
+    decay_scan_kernel<T, KRV, (KRV > 32 ? 8 : 16), BON><<<dim3(num_seqs, heads * colblocks, GZ), kLaCols * kLaLanes, 0, st>>>(                                           \
         (const T *)q, q_token, q_head, (const T *)k, k_token, k_head, (const T *)v, v_token, v_head, z, z_token, (const T *)z_bias, z ? 1.0f / tau : 0.f, head_decay, \
-        rope_cos, rope_sin, rope_dims, rope_interleaved, q_scale, heads, dk, dv, seq_info, state, slot_stride, num_slots, out, PASS, max_segments, seg_state, seg_decay)
+        rope_cos, rope_sin, rope_dims, rope_interleaved, q_scale, heads, dk, dv, seq_info, state, slot_stride, num_slots, out, PASS, max_segments, seg_state, seg_decay, \
+        decay_kind, (const T *)a_log, (const T *)bonus, qk_heads, (const T *)skip)
+#define TLB_DS_K(KRV, PASS, GZ) do { if (bonus) TLB_DS_B(KRV, PASS, GZ, true); else TLB_DS_B(KRV, PASS, GZ, false); } while (0)
 #define TLB_DS(PASS, GZ) TLB_DISPATCH(dtype, "decay_scan", if (kr <= 8) TLB_DS_K(8, PASS, GZ); else if (kr <= 16) TLB_DS_K(16, PASS, GZ); else if (kr <= 32) TLB_DS_K(32, PASS, GZ); else TLB_DS_K(64, PASS, GZ))
     if (!segmented) {
         TLB_DS(0, 1);
@@ -264,17 +296,18 @@ int tlb_decay_scan(const void *q, long long q_token, long long q_head, const voi
     TL_LAUNCH_CHECK("decay_scan (outputs)");
 #undef TLB_DS
 #undef TLB_DS_K
+#undef TLB_DS_B
     return TL_OK;
 }
 
 int tlb_head_norm_gate(const float *o, const void *w, float eps, const void *gate, long long g_token, int act, void *out, int tokens, int heads,
-                       int dv, int dtype, void *stream) {
+                       int dv, int wide_weight, int gate_first, int dtype, void *stream) {
     if (tokens <= 0) return TL_OK;
     if (!o || !out || heads <= 0 || dv <= 0 || act < 0 || act > 2) return tl::fail(TL_EINVAL, "head_norm_gate: bad argument");
     long long rows = (long long)tokens * heads;
     TLB_DISPATCH(dtype, "head_norm_gate",
                  head_norm_gate_kernel<T><<<(unsigned)((rows + 3) / 4), 128, 0, as_stream(stream)>>>(o, (const T *)w, eps, (const T *)gate, g_token, act,
-                                                                                                    (T *)out, rows, heads, dv));
+                                                                                                    (T *)out, rows, heads, dv, wide_weight, gate_first));
     TL_LAUNCH_CHECK("head_norm_gate");
     return TL_OK;
 }

@@ -7,8 +7,10 @@
 //   mask 0  every earlier position (causal)
 //   mask 1  itself and the size-1 positions before it (sliding window)
 //   mask 2  the earlier positions of its own block of `size` positions, blocks counted from position 0 (chunks)
-// and so are a tanh soft cap on the scaled scores, a sink (one more term exp(0) in the softmax's denominator that
-// carries no value) and a per-head output gate (the output of head h times sigmoid(gate[t, h])).
+// and so are a tanh soft cap on the scaled scores, a sink (one more term in the softmax's denominator that carries no
+// value: exp(0), or exp(head_bias[h]) with a learned number per head) and a per-head output gate (the output of head h
+// times sigmoid(gate[t, h])).  weights 1 replaces the softmax: a visible key weighs sigmoid(score + head_bias[h]) and
+// nothing is normalised over the keys.
 // Scores, the running maximum / sum and the accumulators are fp32; cache rows are converted as they are staged, so the
 // same kernel serves the bf16 and the fp32 cache.  Key tiles are 32-aligned in absolute positions and taken in
 // ascending order, so a row's sum does not depend on where a prompt was cut or on what shares the launch.
@@ -35,7 +37,8 @@ __global__ void __launch_bounds__(kPaWarps * 32)
 paged_attention_kernel(const T *__restrict__ q, long long q_token, long long q_head, const T *__restrict__ slab, int num_pages, int page_size,
                        int row_width, int dk, int dv, int heads, int kv_heads, const int32_t *__restrict__ block_table, int max_pages,
                        const int32_t *__restrict__ tiles, const int32_t *__restrict__ tok_pos, int mask, int mask_size, float scale, float softcap,
-                       int sink, const T *__restrict__ gate, long long g_token, T *__restrict__ out, long long o_token, long long o_head) {
+                       int sink, const T *__restrict__ gate, long long g_token, T *__restrict__ out, long long o_token, long long o_head,
+                       const float *__restrict__ head_bias, int weights) {
     extern __shared__ float smem[];
     const int kstride = dk + 1;            // +1 breaks the bank conflict of lane = key reads
     float *sq = smem;                      // [kPaRows][dk]
@@ -64,8 +67,10 @@ paged_attention_kernel(const T *__restrict__ q, long long q_token, long long q_h
     const bool live0 = tq0 < count && (r0 % hp) < nheads, live1 = tq1 < count && (r1 % hp) < nheads;
     const int p0 = pos0 + tq0, p1 = pos0 + tq1;
 
-    // a sink is a key of score 0 without a value: the running maximum starts at 0 and the sum at 1
-    float m0 = sink ? 0.f : -INFINITY, m1 = m0, l0 = sink ? 1.f : 0.f, l1 = l0;
+    // a sink is a key of score 0 (or head_bias[h]) without a value: the running maximum starts there and the sum at 1
+    const float hb0 = head_bias && live0 ? head_bias[head0 + r0 % hp] : 0.f, hb1 = head_bias && live1 ? head_bias[head0 + r1 % hp] : 0.f;
+    float m0 = sink ? hb0 : -INFINITY, m1 = sink ? hb1 : -INFINITY, l0 = sink ? 1.f : 0.f, l1 = l0;
+    if (weights == 1) m0 = m1 = 0.f, l0 = l1 = 1.f;
     float acc0[VL], acc1[VL];
 #pragma unroll
     for (int i = 0; i < VL; ++i) acc0[i] = acc1[i] = 0.f;
@@ -106,17 +111,23 @@ paged_attention_kernel(const T *__restrict__ q, long long q_token, long long q_h
         if (softcap > 0.f) s0 = softcap * tanhf(s0 / softcap), s1 = softcap * tanhf(s1 / softcap);
         bool vis0 = live0 && key <= hi && pa_visible(p0, key, mask, mask_size);
         bool vis1 = live1 && key <= hi && pa_visible(p1, key, mask, mask_size);
-        s0 = vis0 ? s0 : -INFINITY;
-        s1 = vis1 ? s1 : -INFINITY;
-        float n0 = fmaxf(m0, warp_max(s0)), n1 = fmaxf(m1, warp_max(s1));
-        float a0 = n0 == -INFINITY ? 1.f : expf(m0 - n0), a1 = n1 == -INFINITY ? 1.f : expf(m1 - n1);
-        float e0 = vis0 ? expf(s0 - n0) : 0.f, e1 = vis1 ? expf(s1 - n1) : 0.f;
-        l0 = l0 * a0 + warp_sum(e0);
-        l1 = l1 * a1 + warp_sum(e1);
-        m0 = n0;
-        m1 = n1;
+        float e0, e1;
+        if (weights == 1) {
+            e0 = vis0 ? 1.0f / (1.0f + expf(-(s0 + hb0))) : 0.f;
+            e1 = vis1 ? 1.0f / (1.0f + expf(-(s1 + hb1))) : 0.f;
+        } else {
+            s0 = vis0 ? s0 : -INFINITY;
+            s1 = vis1 ? s1 : -INFINITY;
+            float n0 = fmaxf(m0, warp_max(s0)), n1 = fmaxf(m1, warp_max(s1));
+            float a0 = n0 == -INFINITY ? 1.f : expf(m0 - n0), a1 = n1 == -INFINITY ? 1.f : expf(m1 - n1);
+            e0 = vis0 ? expf(s0 - n0) : 0.f, e1 = vis1 ? expf(s1 - n1) : 0.f;
+            l0 = l0 * a0 + warp_sum(e0);
+            l1 = l1 * a1 + warp_sum(e1);
+            m0 = n0;
+            m1 = n1;
 #pragma unroll
-        for (int i = 0; i < VL; ++i) acc0[i] *= a0, acc1[i] *= a1;
+            for (int i = 0; i < VL; ++i) acc0[i] *= a0, acc1[i] *= a1;
+        }
         for (int j = 0; j < kPaKeys; ++j) {
             float w0 = __shfl_sync(0xffffffffu, e0, j), w1 = __shfl_sync(0xffffffffu, e1, j);
             const float *vrow = sv + j * dv;
@@ -194,7 +205,7 @@ template <typename T, int VL>
 static int pa_launch(const void *q, long long q_token, long long q_head, const void *slab, int num_pages, int page_size, int dk, int dv, int heads,
                      int kv_heads, const int32_t *block_table, int max_pages, const int32_t *tiles, int num_tiles, const int32_t *tok_pos, int mask,
                      int mask_size, float scale, float softcap, int sink, const void *gate, long long g_token, void *out, long long o_token,
-                     long long o_head, cudaStream_t st) {
+                     long long o_head, const float *head_bias, int weights, cudaStream_t st) {
     size_t smem = ((size_t)kPaRows * dk + (size_t)kPaKeys * (dk + 1) + (size_t)kPaKeys * dv) * sizeof(float);
     auto kernel = paged_attention_kernel<T, VL>;
     if (smem > 48 * 1024) {
@@ -206,7 +217,7 @@ static int pa_launch(const void *q, long long q_token, long long q_head, const v
     dim3 grid(num_tiles, kv_heads * ceil_div(group, pa_heads_per_cta(group)));
     kernel<<<grid, kPaWarps * 32, smem, st>>>((const T *)q, q_token, q_head, (const T *)slab, num_pages, page_size, kv_heads * (dk + dv), dk, dv, heads,
                                               kv_heads, block_table, max_pages, tiles, tok_pos, mask, mask_size, scale, softcap, sink, (const T *)gate,
-                                              g_token, (T *)out, o_token, o_head);
+                                              g_token, (T *)out, o_token, o_head, head_bias, weights);
     return TL_OK;
 }
 
@@ -224,8 +235,9 @@ int tlb_paged_attention_tile_tokens(int heads, int kv_heads) {
 int tlb_paged_attention(const void *q, long long q_token, long long q_head, const void *slab, int num_pages, int page_size, int dk, int dv, int heads,
                         int kv_heads, const int32_t *block_table, int max_pages, const int32_t *tiles, int num_tiles, const int32_t *tok_pos, int mask,
                         int mask_size, float scale, float softcap, int sink, const void *gate, long long g_token, void *out, long long o_token,
-                        long long o_head, int dtype, void *stream) {
+                        long long o_head, const float *head_bias, int weights, int dtype, void *stream) {
     if (num_tiles <= 0) return TL_OK;
+    if (weights < 0 || weights > 1 || (weights == 1 && (sink || softcap > 0.f))) return tl::fail(TL_EINVAL, "paged_attention: bad weights mode");
     if (!q || !slab || !block_table || !tiles || !tok_pos || !out || dk <= 0 || dv <= 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads ||
         max_pages <= 0 || num_pages <= 0)
         return tl::fail(TL_EINVAL, "paged_attention: bad argument");
@@ -237,7 +249,7 @@ int tlb_paged_attention(const void *q, long long q_token, long long q_head, cons
     int rc = TL_OK;
 #define TLB_PA(V)                                                                                                                                   \
     rc = pa_launch<T, V>(q, q_token, q_head, slab, num_pages, page_size, dk, dv, heads, kv_heads, block_table, max_pages, tiles, num_tiles, tok_pos, \
-                         mask, mask_size, scale, softcap, sink, gate, g_token, out, o_token, o_head, st)
+                         mask, mask_size, scale, softcap, sink, gate, g_token, out, o_token, o_head, head_bias, weights, st)
     TLB_DISPATCH(dtype, "paged_attention", if (vl <= 1) TLB_PA(1); else if (vl <= 2) TLB_PA(2); else if (vl <= 4) TLB_PA(4); else if (vl <= 8) TLB_PA(8);
                  else TLB_PA(16));
 #undef TLB_PA

@@ -62,7 +62,8 @@ paged_attention_mma_kernel(const bf16 *__restrict__ q, long long q_token, long l
                            const int32_t *__restrict__ block_table, int max_pages, const int32_t *__restrict__ tiles, const int32_t *__restrict__ tok_pos,
                            int mask, int mask_size, float scale, float softcap, int sink, const bf16 *__restrict__ gate, long long g_token,
                            bf16 *__restrict__ out, long long o_token, long long o_head, int k_stride, int v_stride /* shared-memory row strides */,
-                           float *__restrict__ partial /* split results, or NULL */) {
+                           float *__restrict__ partial /* split results, or NULL */, const float *__restrict__ head_bias /* [heads] or NULL */,
+                           int weights /* 0 softmax, 1 sigmoid(score + head_bias) without normalisation */) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16 *sq = reinterpret_cast<bf16 *>(smem_raw);              // [32][k_stride]
     bf16 *skv = sq + kGRows * k_stride;                         // [2] x ([32][k_stride] keys | [32][v_stride] values)
@@ -128,10 +129,14 @@ paged_attention_mma_kernel(const bf16 *__restrict__ q, long long q_token, long l
     // softmax state of the row this lane works on (a warp owns 4 rows, 8 lanes each; uniform over the 8 lanes)
     const bool sunk = sink && blockIdx.z == 0;  // with the key range split over gridDim.z CTAs the sink's term is counted once
     float m_row = sunk ? 0.f : -INFINITY, l_row = sunk ? 1.f : 0.f;
+    float hb = 0.f;  // the row's head's learned number: the sink's score, or the offset inside the sigmoid
     int see_lo = 1, see_hi = 0;  // the keys this row may see (none for a padding row)
     {
         int r = warp * 4 + (lane >> 3), tq = r / hp, hh = r % hp;
         if (tq < count && hh < nheads) {
+            if (head_bias) hb = head_bias[head0 + hh];
+            if (sunk) m_row = hb;
+            if (weights == 1) m_row = 0.f, l_row = blockIdx.z == 0 ? 1.f : 0.f;
             see_hi = pos0 + tq;
             see_lo = mask == 1 ? max(0, see_hi - mask_size + 1) : mask == 2 ? see_hi / mask_size * mask_size : 0;
         }
@@ -197,22 +202,29 @@ paged_attention_mma_kernel(const bf16 *__restrict__ q, long long q_token, long l
                 sv4[j] = vis ? s : -INFINITY;
                 mx = fmaxf(mx, sv4[j]);
             }
+            if (weights == 1) {  // every visible key by itself: no maximum, no sum, nothing to rescale
 #pragma unroll
-            for (int o = 4; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-            float m_new = fmaxf(m_row, mx);
-            float alpha = m_new == -INFINITY ? 1.f : expf(m_row - m_new);
-            float sum = 0.f;
+                for (int j = 0; j < kGKeys / 8; ++j)
+                    sp[r * kGSP + lq + 8 * j] = __float2bfloat16_rn(sv4[j] == -INFINITY ? 0.f : 1.0f / (1.0f + expf(-(sv4[j] + hb))));
+                if (lq == 0) s_alpha[r] = 1.f;
+            } else {
 #pragma unroll
-            for (int j = 0; j < kGKeys / 8; ++j) {
-                bf16 pb = __float2bfloat16_rn(sv4[j] == -INFINITY ? 0.f : expf(sv4[j] - m_new));
-                sum += __bfloat162float(pb);  // the rounded probability: numerator and denominator see the same weights
-                sp[r * kGSP + lq + 8 * j] = pb;
+                for (int o = 4; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+                float m_new = fmaxf(m_row, mx);
+                float alpha = m_new == -INFINITY ? 1.f : expf(m_row - m_new);
+                float sum = 0.f;
+#pragma unroll
+                for (int j = 0; j < kGKeys / 8; ++j) {
+                    bf16 pb = __float2bfloat16_rn(sv4[j] == -INFINITY ? 0.f : expf(sv4[j] - m_new));
+                    sum += __bfloat162float(pb);  // the rounded probability: numerator and denominator see the same weights
+                    sp[r * kGSP + lq + 8 * j] = pb;
+                }
+#pragma unroll
+                for (int o = 4; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+                l_row = l_row * alpha + sum;
+                m_row = m_new;
+                if (lq == 0) s_alpha[r] = alpha;
             }
-#pragma unroll
-            for (int o = 4; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-            l_row = l_row * alpha + sum;
-            m_row = m_new;
-            if (lq == 0) s_alpha[r] = alpha;
         }
         __syncthreads();
 
@@ -351,8 +363,10 @@ size_t tlb_paged_attention_mma_workspace(int num_tiles, int heads, int kv_heads,
 int tlb_paged_attention_mma(const void *q, long long q_token, long long q_head, const void *slab, int num_pages, int page_size, int dk, int dv, int heads,
                             int kv_heads, const int32_t *block_table, int max_pages, const int32_t *tiles, int num_tiles, const int32_t *tok_pos,
                             int mask, int mask_size, float scale, float softcap, int sink, const void *gate, long long g_token, void *out,
-                            long long o_token, long long o_head, int splits, void *workspace, size_t workspace_bytes, void *stream) {
+                            long long o_token, long long o_head, int splits, void *workspace, size_t workspace_bytes, const float *head_bias,
+                            int weights, void *stream) {
     if (num_tiles <= 0) return TL_OK;
+    if (weights < 0 || weights > 1 || (weights == 1 && (sink || softcap > 0.f))) return tl::fail(TL_EINVAL, "paged_attention_mma: bad weights mode");
     if (!q || !slab || !block_table || !tiles || !tok_pos || !out || heads <= 0 || kv_heads <= 0 || heads % kv_heads || max_pages <= 0 || num_pages <= 0)
         return tl::fail(TL_EINVAL, "paged_attention_mma: bad argument");
     if (!tlb_paged_attention_mma_supported(dk, dv, kv_heads, page_size))
@@ -381,7 +395,7 @@ int tlb_paged_attention_mma(const void *q, long long q_token, long long q_head, 
         }                                                                                                                                        \
         kernel<<<grid, kGWarps * 32, smem, st>>>((const bf16 *)q, q_token, q_head, (const bf16 *)slab, num_pages, page_size, kv_heads * (dk + dv), dk, dv, \
                                                  heads, kv_heads, hp, block_table, max_pages, tiles, tok_pos, mask, mask_size, scale, softcap, sink,    \
-                                                 (const bf16 *)gate, g_token, (bf16 *)out, o_token, o_head, k_stride, v_stride, part);                  \
+                                                 (const bf16 *)gate, g_token, (bf16 *)out, o_token, o_head, k_stride, v_stride, part, head_bias, weights); \
     } while (0)
     if (pairs == 1) TLB_PAM(1);
     else if (pairs == 2) TLB_PAM(2);

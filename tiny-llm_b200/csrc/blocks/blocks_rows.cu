@@ -237,13 +237,13 @@ __device__ __forceinline__ float act_apply(float z, int act) {
     return 0.5f * z * (1.0f + tanhf(inner));
 }
 
-// out = act(x) elementwise; act 0 = silu, 1 = gelu (tanh form), 2 = squared relu.
+// out = act(x) elementwise; act 0 = silu, 1 = gelu (tanh form), 2 = squared relu, 4 = tanh.
 template <typename T>
 __global__ void act_rows_kernel(const T *__restrict__ x, T *__restrict__ out, long long total, int act) {
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     float z = to_f(x[i]);
-    out[i] = from_f<T>(act == 2 ? (z > 0.f ? z * z : 0.f) : act_apply(z, act));
+    out[i] = from_f<T>(act == 2 ? (z > 0.f ? z * z : 0.f) : act == 4 ? tanhf(z) : act_apply(z, act));
 }
 
 // x <- cap * tanh(x / cap), fp32 in place.
@@ -261,12 +261,17 @@ __global__ void cast_rows_kernel(const float *__restrict__ src, T *__restrict__ 
 }
 
 template <typename T>
-__global__ void gated_act_kernel(const T *__restrict__ gu, T *__restrict__ out, long long total, int width, int act) {
+__global__ void gated_act_kernel(const T *__restrict__ gu, T *__restrict__ out, long long total, int width, int act, float limit, float slope) {
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     long long row = i / width;
     int j = (int)(i - row * width);
     float g = to_f(gu[row * 2 * width + j]), u = to_f(gu[row * 2 * width + width + j]);
+    if (act == 3) {  // clamped: the gate from above, the other half on both sides; g sigmoid(slope g) (u + 1)
+        g = fminf(g, limit), u = fminf(fmaxf(u, -limit), limit);
+        out[i] = from_f<T>(g / (1.0f + expf(-slope * g)) * (u + 1.0f));
+        return;
+    }
     out[i] = from_f<T>(act_apply(g, act) * u);
 }
 
@@ -307,7 +312,7 @@ using namespace tlb;
 
 extern "C" {
 
-int tlb_abi_version(void) { return 4; }
+int tlb_abi_version(void) { return 5; }
 const char *tlb_last_error(void) { return tl::g_error; }
 long long tlb_launch_count(void) { return tl::g_launches.load(std::memory_order_relaxed); }
 
@@ -396,19 +401,19 @@ int tlb_latent_prepare(const void *down, long long down_stride, const void *norm
     return TL_OK;
 }
 
-int tlb_gated_act(const void *gu, void *out, int rows, int width, int act, int dtype, void *stream) {
+int tlb_gated_act(const void *gu, void *out, int rows, int width, int act, float limit, float slope, int dtype, void *stream) {
     if (rows <= 0 || width <= 0) return TL_OK;
-    if (!gu || !out || (act != 0 && act != 1)) return tl::fail(TL_EINVAL, "gated_act: bad argument");
+    if (!gu || !out || (act != 0 && act != 1 && act != 3) || (act == 3 && !(limit > 0.f))) return tl::fail(TL_EINVAL, "gated_act: bad argument");
     long long total = (long long)rows * width;
     TLB_DISPATCH(dtype, "gated_act",
-                 gated_act_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, as_stream(stream)>>>((const T *)gu, (T *)out, total, width, act));
+                 gated_act_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, as_stream(stream)>>>((const T *)gu, (T *)out, total, width, act, limit, slope));
     TL_LAUNCH_CHECK("gated_act");
     return TL_OK;
 }
 
 int tlb_act_rows(const void *x, void *out, int rows, int width, int act, int dtype, void *stream) {
     if (rows <= 0 || width <= 0) return TL_OK;
-    if (!x || !out || act < 0 || act > 2) return tl::fail(TL_EINVAL, "act_rows: bad argument");
+    if (!x || !out || act < 0 || act > 4 || act == 3) return tl::fail(TL_EINVAL, "act_rows: bad argument");
     long long total = (long long)rows * width;
     TLB_DISPATCH(dtype, "act_rows", act_rows_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, as_stream(stream)>>>((const T *)x, (T *)out, total, act));
     TL_LAUNCH_CHECK("act_rows");

@@ -50,6 +50,7 @@ BLOCKS_SOURCES = [
     "blocks/blocks_paged_attention_mma.cu",
     "blocks/blocks_linear_attention.cu",
     "blocks/blocks_delta_rule.cu",
+    "blocks/blocks_streams.cu",
 ]
 
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")

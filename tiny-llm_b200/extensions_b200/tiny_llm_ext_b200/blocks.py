@@ -3,7 +3,7 @@ an fp32 residual stream, rotary positions, the paged latent cache, latent attent
 activations and the mixture-of-experts kernels.  Arguments are contiguous CUDA ``torch.Tensor`` s (strided where the
 function says so); every call enqueues on the current stream.  There is no CPU path.
 
-The library is built on first use when it is missing (three small translation units, a few seconds of nvcc)."""
+The library is built on first use when it is missing (a handful of translation units, compiled side by side)."""
 
 from __future__ import annotations
 
@@ -30,37 +30,40 @@ _SIGNATURES = {
     "tlb_rope_table": (_I, [_VP, _I, _I, _D, _D, _VP, _VP, _VP]),
     "tlb_latent_append": (_I, [_VP, _VP, _F, _I, _I, _I, _I, _D, _VP, _VP, _VP, _I, _I, _I, _VP, _I, _I, _VP]),
     "tlb_latent_prepare": (_I, [_VP, _LL, _VP, _F, _I, _I, _I, _I, _D, _VP, _VP, _VP, _I, _I, _I, _VP, _VP, _LL, _I, _I, _I, _I, _I, _VP]),
-    "tlb_latent_attention": (_I, [_VP, _LL, _LL, _VP, _LL, _LL, _VP, _I, _I, _I, _I, _VP, _I, _VP, _I, _VP, _I, _I, _F, _VP, _LL, _LL, _I, _VP]),
+    "tlb_latent_attention": (_I, [_VP, _LL, _LL, _VP, _LL, _LL, _VP, _I, _I, _I, _I, _VP, _I, _VP, _I, _VP, _I, _I, _F, _VP, _LL, _LL, _VP, _I, _VP]),
     "tlb_latent_attention_mma_tile_tokens": (_I, [_I]),
     "tlb_latent_attention_mma_supported": (_I, [_I, _I, _I]),
     "tlb_latent_attention_mma": (_I, [_VP, _LL, _LL, _VP, _LL, _LL, _VP, _I, _I, _I, _I, _VP, _I, _VP, _I, _VP, _I, _I, _F, _VP, _LL, _LL, _I, _VP,
-                                      ctypes.c_size_t, _VP]),
+                                      ctypes.c_size_t, _VP, _VP]),
     "tlb_latent_attention_mma_workspace": (ctypes.c_size_t, [_I, _I, _I, _I]),
-    "tlb_gated_act": (_I, [_VP, _VP, _I, _I, _I, _I, _VP]),
+    "tlb_gated_act": (_I, [_VP, _VP, _I, _I, _I, _F, _F, _I, _VP]),
+    "tlb_streams_step": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _F, _VP, _I, _I, _I, _I, _VP]),
+    "tlb_shift_mix": (_I, [_VP, _LL, _VP, _I, _I, _VP, _I, _I, _VP, _LL, _I, _VP, _LL, _I, _VP]),
     "tlb_moe_route": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _I, _VP, _F, _VP, _VP, _I, _VP]),
     "tlb_moe_up": (_I, [_VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _I, _I, _VP, _I, _VP]),
     "tlb_moe_scale_rows": (_I, [_VP, _VP, _VP, _I, _I, _I, _I, _VP]),
     "tlb_add_norm": (_I, [_VP, _VP, _I, _VP, _VP, _F, _VP, _I, _I, _I, _VP]),
     "tlb_norm_mix2": (_I, [_VP, _VP, _VP, _VP, _F, _F, _VP, _I, _I, _I, _VP]),
     "tlb_paged_attention_tile_tokens": (_I, [_I, _I]),
-    "tlb_paged_attention": (_I, [_VP, _LL, _LL, _VP, _I, _I, _I, _I, _I, _I, _VP, _I, _VP, _I, _VP, _I, _I, _F, _F, _I, _VP, _LL, _VP, _LL, _LL, _I, _VP]),
+    "tlb_paged_attention": (_I, [_VP, _LL, _LL, _VP, _I, _I, _I, _I, _I, _I, _VP, _I, _VP, _I, _VP, _I, _I, _F, _F, _I, _VP, _LL, _VP, _LL, _LL, _VP, _I, _I,
+                                 _VP]),
     "tlb_paged_attention_mma_tile_tokens": (_I, [_I, _I]),
     "tlb_paged_attention_mma_supported": (_I, [_I, _I, _I, _I]),
     "tlb_paged_attention_mma": (_I, [_VP, _LL, _LL, _VP, _I, _I, _I, _I, _I, _I, _VP, _I, _VP, _I, _VP, _I, _I, _F, _F, _I, _VP, _LL, _VP, _LL, _LL, _I, _VP,
-                                     ctypes.c_size_t, _VP]),
+                                     ctypes.c_size_t, _VP, _I, _VP]),
     "tlb_paged_attention_mma_workspace": (ctypes.c_size_t, [_I, _I, _I, _I, _I]),
     "tlb_kv_prepare": (_I, [_VP, _LL, _LL, _I, _VP, _VP, _LL, _LL, _VP, _LL, _LL, _I, _I, _I, _VP, _F, _VP, _VP, _VP, _I, _I, _I, _VP, _I, _I, _VP]),
     "tlb_decay_scan_workspace": (ctypes.c_size_t, [_I, _I, _I, _I, _I]),
     "tlb_decay_scan": (_I, [_VP, _LL, _LL, _VP, _LL, _LL, _VP, _LL, _LL, _VP, _LL, _VP, _F, _VP, _VP, _VP, _I, _I, _F, _I, _I, _I, _VP, _I, _I, _VP, _LL, _I,
-                            _VP, _VP, ctypes.c_size_t, _I, _VP]),
+                            _VP, _VP, ctypes.c_size_t, _I, _VP, _VP, _I, _VP, _I, _VP]),
     "tlb_delta_scan_workspace": (ctypes.c_size_t, [_I, _I, _I, _I, _I]),
     "tlb_delta_scan": (_I, [_VP, _LL, _LL, _VP, _LL, _LL, _VP, _LL, _LL, _VP, _LL, _VP, _I, _LL, _I, _VP, _VP, _F, _F, _I, _I, _I, _I, _VP, _I, _I, _VP, _LL,
                             _I, _VP, _VP, ctypes.c_size_t, _I, _VP]),
-    "tlb_short_conv": (_I, [_VP, _LL, _VP, _I, _I, _I, _VP, _I, _I, _VP, _LL, _I, _VP, _I, _VP]),
+    "tlb_short_conv": (_I, [_VP, _LL, _VP, _VP, _I, _I, _I, _I, _VP, _I, _I, _VP, _LL, _I, _VP, _I, _VP]),
     "tlb_act_rows": (_I, [_VP, _VP, _I, _I, _I, _I, _VP]),
     "tlb_softcap_rows": (_I, [_VP, _I, _I, _F, _VP]),
     "tlb_cast_rows": (_I, [_VP, _VP, _LL, _I, _I, _I, _VP]),
-    "tlb_head_norm_gate": (_I, [_VP, _VP, _F, _VP, _LL, _I, _VP, _I, _I, _I, _I, _VP]),
+    "tlb_head_norm_gate": (_I, [_VP, _VP, _F, _VP, _LL, _I, _VP, _I, _I, _I, _I, _I, _I, _VP]),
     "tlb_moe_max_rows": (_LL, [_I, _I, _I, _I]),
     "tlb_moe_sort": (_I, [_VP, _I, _I, _I, _I, _VP, _VP, _VP, _VP]),
     "tlb_moe_gate_up": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _I, _I, _I, _I, _I, _I, _I, _VP, _I, _VP]),
@@ -70,10 +73,12 @@ _SIGNATURES = {
 }
 EXPORTED_SYMBOLS = tuple(_SIGNATURES)
 
-ABI_VERSION = 4
+ABI_VERSION = 5
 ATTENTION_TILE_TOKENS = 4
 MOE_TILE_ROWS = 32
-ACT_SILU, ACT_GELU_TANH, ACT_RELU_SQUARED = 0, 1, 2
+ACT_SILU, ACT_GELU_TANH, ACT_RELU_SQUARED, ACT_CLAMPED_SWISH, ACT_TANH = 0, 1, 2, 3, 4
+WEIGHTS_SOFTMAX, WEIGHTS_SIGMOID = 0, 1
+DECAY_SIGMOID, DECAY_DOUBLE_EXP, DECAY_STEP = 0, 2, 3
 MASK_CAUSAL, MASK_WINDOW, MASK_CHUNK = 0, 1, 2
 SCORE_SOFTMAX, SCORE_SIGMOID, SCORE_SOFTMAX_ALL = 0, 1, 2
 _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 2}
@@ -250,6 +255,22 @@ def latent_prepare(qd, norm_weight, eps, *, heads, dim, rot_dim, rank, rot_dims,
                                         _ptr(qd), total, heads, dim + rot_dim, dim, T, _code(qd.dtype), _stream(qd)))
 
 
+def latent_prepare_parts(q, down, norm_weight, eps, *, heads, dim, rot_dim, rank, rot_dims, interleaved, base, tok_pos, tok_seq, block_table, slab):
+    """``latent_prepare`` for queries and down projection that are separate matrices (views with unit inner stride):
+    ``q [T, heads * (dim + rot_dim)]`` rotated in place, ``down [T, rank + rot_dim]`` normed, rotated and stored."""
+    _gpu("latent_prepare", q, down, norm_weight, tok_pos, tok_seq, block_table, slab)
+    _contig("latent_prepare", norm_weight, tok_pos, tok_seq, block_table, slab)
+    T = q.shape[0]
+    P, page_size, width = slab.shape
+    if q.shape != (T, heads * (dim + rot_dim)) or down.shape != (T, width) or width != rank + rot_dim or q.stride(1) != 1 or down.stride(1) != 1:
+        raise RuntimeError("latent_prepare: queries, down projection and slab do not match")
+    if not (slab.dtype == q.dtype == down.dtype == norm_weight.dtype) or norm_weight.numel() != rank:
+        raise RuntimeError("latent_prepare: one dtype, and a weight of [rank]")
+    _check(library().tlb_latent_prepare(_ptr(down), down.stride(0), _ptr(norm_weight), float(eps), rank, rot_dim, rot_dims, int(interleaved), float(base),
+                                        _ptr(tok_pos), _ptr(tok_seq), _ptr(block_table), block_table.shape[1], P, page_size, _ptr(slab), _ptr(q),
+                                        q.stride(0), heads, dim + rot_dim, dim, T, _code(q.dtype), _stream(q)))
+
+
 def attention_kernel(dtype, heads: int, rank: int, rot: int, page_size: int) -> tuple[str, int]:
     """Which latent-attention kernel serves these sizes, and the most tokens one entry of its ``tiles`` may hold:
     ``("mma", 32 // min(heads, 32))`` for a bf16 cache the tensor-core kernel can take (32 query rows per CTA), else
@@ -274,12 +295,16 @@ def attention_splits(num_ctas: int, max_context: int, device) -> int:
     return max(1, min(sms // num_ctas, max_context // 128, 32))
 
 
-def latent_attention(q_lat, q_rot, slab, block_table, tiles, tok_pos, *, window: int, scale: float, out, kernel: str = "general", max_context: int = 0):
+def latent_attention(q_lat, q_rot, slab, block_table, tiles, tok_pos, *, window: int, scale: float, out, kernel: str = "general", max_context: int = 0,
+                     sink=None):
     """``q_lat [T, H, rank]``, ``q_rot [T, H, rot]`` and ``out [T, H, rank]`` are views with arbitrary token / head strides
     and unit inner stride; ``tiles [n, 3]`` int32 (first token, count, block-table row) cut for the tile size that
     ``attention_kernel`` gives beside the kernel's name.  ``max_context`` (the longest sequence of the step, 0 = unknown)
-    lets the tensor-core kernel split the key range over several CTAs when the launch alone would leave SMs idle."""
-    _gpu("latent_attention", q_lat, q_rot, slab, block_table, tiles, tok_pos, out)
+    lets the tensor-core kernel split the key range over several CTAs when the launch alone would leave SMs idle.
+    ``sink`` (fp32 ``[H]``): one more term ``exp(sink[h])`` in head h's softmax denominator, without a key or a value."""
+    _gpu("latent_attention", q_lat, q_rot, slab, block_table, tiles, tok_pos, out, sink)
+    if sink is not None and (sink.dtype != torch.float32 or sink.shape != (q_lat.shape[1],) or not sink.is_contiguous()):
+        raise RuntimeError("latent_attention: sink must be float32 [H]")
     _contig("latent_attention", slab, block_table, tiles, tok_pos)
     T, H, rank = q_lat.shape
     P, page_size, width = slab.shape
@@ -300,13 +325,13 @@ def latent_attention(q_lat, q_rot, slab, block_table, tiles, tok_pos, *, window:
         _check(lib.tlb_latent_attention_mma(_ptr(q_lat), q_lat.stride(0), q_lat.stride(1), _ptr(q_rot), q_rot.stride(0), q_rot.stride(1), _ptr(slab), P,
                                             page_size, rank, rot, _ptr(block_table), block_table.shape[1], _ptr(tiles), tiles.shape[0], _ptr(tok_pos),
                                             H, int(window or 0), float(scale), _ptr(out), out.stride(0), out.stride(1), splits, _ptr(ws), nbytes,
-                                            _stream(slab)))
+                                            _ptr(sink), _stream(slab)))
         return out
     if kernel != "general":
         raise RuntimeError(f"latent_attention: unknown kernel {kernel!r}")
     _check(lib.tlb_latent_attention(_ptr(q_lat), q_lat.stride(0), q_lat.stride(1), _ptr(q_rot), q_rot.stride(0), q_rot.stride(1), _ptr(slab), P,
                                     page_size, rank, rot, _ptr(block_table), block_table.shape[1], _ptr(tiles), tiles.shape[0], _ptr(tok_pos),
-                                    H, int(window or 0), float(scale), _ptr(out), out.stride(0), out.stride(1), _code(slab.dtype), _stream(slab)))
+                                    H, int(window or 0), float(scale), _ptr(out), out.stride(0), out.stride(1), _ptr(sink), _code(slab.dtype), _stream(slab)))
     return out
 
 
@@ -314,13 +339,14 @@ def _mma_ok(rank: int, rot: int, page_size: int) -> bool:
     return os.environ.get("TL_LATENT_MMA", "1") != "0" and bool(library().tlb_latent_attention_mma_supported(rank, rot, page_size))
 
 
-def gated_act(gate_up: torch.Tensor, act: int) -> torch.Tensor:
-    """``act(gate) * up`` of ``[rows, 2 * width]`` (gate columns first)."""
+def gated_act(gate_up: torch.Tensor, act: int, limit: float = 0.0, slope: float = 1.0) -> torch.Tensor:
+    """``act(gate) * up`` of ``[rows, 2 * width]`` (gate columns first).  ``ACT_CLAMPED_SWISH``: ``g = min(gate, limit)``,
+    ``u = clamp(up, -limit, limit)``, ``g sigmoid(slope g) (u + 1)``."""
     _gpu("gated_act", gate_up)
     _contig("gated_act", gate_up)
     rows, two = gate_up.shape
     out = torch.empty((rows, two // 2), dtype=gate_up.dtype, device=gate_up.device)
-    _check(library().tlb_gated_act(_ptr(gate_up), _ptr(out), rows, two // 2, act, _code(gate_up.dtype), _stream(gate_up)))
+    _check(library().tlb_gated_act(_ptr(gate_up), _ptr(out), rows, two // 2, act, float(limit), float(slope), _code(gate_up.dtype), _stream(gate_up)))
     return out
 
 
@@ -452,13 +478,16 @@ def kv_prepare(q, k, v, *, q_norm=None, k_norm=None, eps: float = 0.0, tok_pos=N
 
 
 def paged_attention(q, slab, block_table, tiles, tok_pos, *, kv_heads: int, dv: int, mask: int, mask_size: int, scale: float, softcap: float = 0.0,
-                    sink: bool = False, gate=None, out=None, kernel: str = "general", max_context: int = 0):
+                    sink: bool = False, gate=None, out=None, kernel: str = "general", max_context: int = 0, head_bias=None, weights: int = 0):
     """``q [T, H, dk]`` (a view with unit inner stride) against ``slab [P, page, kv_heads * (dk + dv)]`` -> ``out [T, H, dv]``
     (contiguous, the query's dtype).  ``gate [T, H]`` (a view with unit inner stride): logits of a sigmoid output gate.
     ``kernel`` and the tile size of ``tiles`` come from ``paged_attention_kernel``.  ``max_context`` (the longest sequence of
     the step, 0 = unknown) lets the tensor-core kernel split the key range over several CTAs when the launch alone would
-    leave SMs idle."""
-    _gpu("paged_attention", q, slab, block_table, tiles, tok_pos, gate, out)
+    leave SMs idle.  ``head_bias`` (fp32 ``[H]``): with ``sink`` the sink's term is ``exp(head_bias[h])`` instead of ``exp(0)``;
+    with ``weights=WEIGHTS_SIGMOID`` there is no softmax, a visible key weighs ``sigmoid(score + head_bias[h])``."""
+    _gpu("paged_attention", q, slab, block_table, tiles, tok_pos, gate, out, head_bias)
+    if head_bias is not None and (head_bias.dtype != torch.float32 or head_bias.shape != (q.shape[1],) or not head_bias.is_contiguous()):
+        raise RuntimeError("paged_attention: head_bias must be float32 [H]")
     _contig("paged_attention", slab, block_table, tiles, tok_pos)
     T, H, dk = q.shape
     P, page_size, width = slab.shape
@@ -482,36 +511,48 @@ def paged_attention(q, slab, block_table, tiles, tok_pos, *, kv_heads: int, dv: 
                                            block_table.shape[1], _ptr(tiles), tiles.shape[0], _ptr(tok_pos), int(mask), int(mask_size),
                                            float(scale), float(softcap or 0.0), int(bool(sink)), _ptr(gate),
                                            gate.stride(0) if gate is not None else 0, _ptr(out), out.stride(0), out.stride(1), splits, _ptr(ws), nbytes,
-                                           _stream(q)))
+                                           _ptr(head_bias), int(weights), _stream(q)))
         return out
     if kernel != "general":
         raise RuntimeError(f"paged_attention: unknown kernel {kernel!r}")
     _check(library().tlb_paged_attention(_ptr(q), q.stride(0), q.stride(1), _ptr(slab), P, page_size, dk, dv, H, kv_heads, _ptr(block_table),
                                          block_table.shape[1], _ptr(tiles), tiles.shape[0], _ptr(tok_pos), int(mask), int(mask_size), float(scale),
                                          float(softcap or 0.0), int(bool(sink)), _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(out),
-                                         out.stride(0), out.stride(1), _code(q.dtype), _stream(q)))
+                                         out.stride(0), out.stride(1), _ptr(head_bias), int(weights), _code(q.dtype), _stream(q)))
     return out
 
 
 def decay_scan(q, k, v, z, z_bias, *, tau: float = 1.0, q_scale: float, seq_info, state, out=None, max_tokens: int | None = None, head_decay=None,
-               rope=None, rope_dims: int = 0, rope_interleaved: bool = False):
+               rope=None, rope_dims: int = 0, rope_interleaved: bool = False, decay_kind: int = 0, a_log=None, bonus=None, skip=None):
     """Linear attention with per-channel decay ``sigmoid(z + z_bias)^(1/tau)``: ``q, k [T, H, dk]``, ``v [T, H, dv]`` views,
     ``z [T, H * dk]`` fp32, ``seq_info [S, 4]`` int32 (first token, count, start position, slot), ``state [slots, H, dk, dv]``
     fp32 (a view whose slots may be further apart) -> fp32 ``[T, H, dv]``.  ``max_tokens``: the largest count in
     ``seq_info`` (default: all tokens); portions longer than a segment run as parallel segments over a workspace.
     ``head_decay`` (fp32 ``[H]``) replaces the logits by one fixed decay per head (``z`` None).  ``rope`` = (cos, sin) tables
     of ``rope_table`` for this step's tokens: the first ``rope_dims`` entries of every head of q and k are rotated in fp32
-    on their way in."""
-    _gpu("decay_scan", q, k, v, z, z_bias, seq_info, state, out, head_decay)
-    T, H, dk = q.shape
-    dv = v.shape[2]
-    if k.shape != (T, H, dk) or v.shape[:2] != (T, H):
+    on their way in.  ``decay_kind``: ``DECAY_SIGMOID`` as above; ``DECAY_DOUBLE_EXP`` = ``exp(-exp(z + z_bias))`` per key channel;
+    ``DECAY_STEP`` = one decay per head and token, ``exp(-exp(a_log[h]) dt)`` with ``dt = softplus(z[t, h] + z_bias[h])``
+    (``z [T, H]``), the key multiplied by ``dt``.  ``q, k`` may have fewer heads than ``v`` (``[T, G, dk]``, head h reads
+    ``h // (H // G)``).  ``skip [H]``: ``out += skip[h] v``.  ``bonus [H, dk]``: the read-out comes before the update and
+    weighs the token's own ``k v^T`` by it."""
+    _gpu("decay_scan", q, k, v, z, z_bias, seq_info, state, out, head_decay, a_log, bonus, skip)
+    T, G, dk = q.shape
+    H, dv = v.shape[1], v.shape[2]
+    if k.shape != (T, G, dk) or v.shape[0] != T or H % G:
         raise RuntimeError("decay_scan: shapes do not match")
-    if head_decay is not None:
+    for name, t, shape in (("a_log", a_log, (H,)), ("bonus", bonus, (H, dk)), ("skip", skip, (H,))):
+        if t is not None and (t.shape != shape or t.dtype != q.dtype or not t.is_contiguous()):
+            raise RuntimeError(f"decay_scan: {name} must be {shape} of the activations' dtype")
+    if decay_kind == DECAY_STEP:
+        if z is None or z.shape != (T, H) or z.dtype != torch.float32 or z.stride(1) != 1 or a_log is None or head_decay is not None:
+            raise RuntimeError("decay_scan: a step decay takes z [T, H] float32 and a_log [H]")
+    elif head_decay is not None:
         if z is not None or head_decay.dtype != torch.float32 or head_decay.shape != (H,) or not head_decay.is_contiguous():
             raise RuntimeError("decay_scan: head_decay must be float32 [H] and replaces z")
     elif z is None or z.shape != (T, H * dk) or z.dtype != torch.float32 or z.stride(1) != 1:
         raise RuntimeError("decay_scan: shapes do not match")
+    if z_bias is not None and (z_bias.dtype != q.dtype or not z_bias.is_contiguous()):
+        raise RuntimeError("decay_scan: z_bias must be contiguous in the activations' dtype")
     cs = sn = None
     if rope_dims:
         cs, sn = rope
@@ -532,25 +573,28 @@ def decay_scan(q, k, v, z, z_bias, *, tau: float = 1.0, q_scale: float, seq_info
     _check(lib.tlb_decay_scan(_ptr(q), q.stride(0), q.stride(1), _ptr(k), k.stride(0), k.stride(1), _ptr(v), v.stride(0), v.stride(1), _ptr(z),
                               z.stride(0) if z is not None else 0, _ptr(z_bias), float(tau), _ptr(head_decay), _ptr(cs), _ptr(sn), int(rope_dims),
                               int(bool(rope_interleaved)), float(q_scale), H, dk, dv, _ptr(seq_info), seq_info.shape[0], longest, _ptr(state),
-                              state.stride(0), state.shape[0], _ptr(out), _ptr(ws), nbytes, _code(q.dtype), _stream(q)))
+                              state.stride(0), state.shape[0], _ptr(out), _ptr(ws), nbytes, int(decay_kind), _ptr(a_log), _ptr(bonus), G, _ptr(skip),
+                              _code(q.dtype), _stream(q)))
     return out
 
 
-def head_norm_gate(o, weight, eps: float, gate=None, act: int = 1):
+def head_norm_gate(o, weight, eps: float, gate=None, act: int = 1, gate_first: bool = False):
     """``o [T, H, dv]`` fp32 -> ``[T, H * dv]`` in the weight's (without one: the gate's) dtype: per-head RMS norm times
     ``weight [dv]`` (None = no weight) times ``silu(gate)`` (``act`` 1), ``sigmoid(gate)`` (2) or ``gate`` (0);
-    ``gate [T, H * dv]`` a view with unit inner stride."""
+    ``gate [T, H * dv]`` a view with unit inner stride.  A weight of ``[H * dv]`` gives every head its own part;
+    ``gate_first``: the gate multiplies ``o`` BEFORE the norm."""
     _gpu("head_norm_gate", o, weight, gate)
     _contig("head_norm_gate", o, weight)
     T, H, dv = o.shape
     if weight is None and gate is None:
         raise RuntimeError("head_norm_gate: a weight or a gate must name the output dtype")
     dtype = weight.dtype if weight is not None else gate.dtype
-    if o.dtype != torch.float32 or (weight is not None and weight.shape != (dv,)) or (gate is not None and (gate.shape != (T, H * dv) or gate.stride(1) != 1 or gate.dtype != dtype)):
+    wide = weight is not None and weight.shape == (H * dv,) and H > 1
+    if o.dtype != torch.float32 or (weight is not None and weight.shape not in ((dv,), (H * dv,))) or (gate is not None and (gate.shape != (T, H * dv) or gate.stride(1) != 1 or gate.dtype != dtype)):
         raise RuntimeError("head_norm_gate: shapes do not match")
     out = torch.empty((T, H * dv), dtype=dtype, device=o.device)
     _check(library().tlb_head_norm_gate(_ptr(o), _ptr(weight), float(eps), _ptr(gate), gate.stride(0) if gate is not None else 0, int(act), _ptr(out),
-                                        T, H, dv, _code(dtype), _stream(o)))
+                                        T, H, dv, int(wide), int(bool(gate_first)), _code(dtype), _stream(o)))
     return out
 
 
@@ -589,12 +633,15 @@ def delta_scan(q, k, v, beta, a, a_log, dt_bias, *, per_channel: bool, q_scale: 
     return out
 
 
-def short_conv(x, taps, *, seq_info, state, max_tokens: int, act: int = 1):
-    """Causal convolution per channel along every sequence, then silu (``act`` 1): ``x [T, C]`` (a view with unit inner
+def short_conv(x, taps, *, seq_info, state, max_tokens: int, act: int = 1, bias=None, add_input: bool = False):
+    """Causal convolution per channel along every sequence (plus ``bias [C]``; plus the input itself, ``add_input``), then silu
+    (``act`` 1) or nothing (0): ``x [T, C]`` (a view with unit inner
     stride), ``taps [C, K]``, ``state [slots, C, K - 1]`` fp32 (a view whose slots may be further apart): the inputs before
     the step's first token, replaced by the step's last ones -> ``[T, C]`` contiguous in x's dtype."""
-    _gpu("short_conv", x, taps, seq_info, state)
-    _contig("short_conv", taps, seq_info)
+    _gpu("short_conv", x, taps, seq_info, state, bias)
+    _contig("short_conv", taps, seq_info, bias)
+    if bias is not None and (bias.shape != (x.shape[1],) or bias.dtype != x.dtype):
+        raise RuntimeError("short_conv: bias must be [C] of x's dtype")
     T, C = x.shape
     K = taps.shape[1]
     if taps.shape[0] != C or taps.dtype != x.dtype or x.stride(1) != 1:
@@ -602,14 +649,14 @@ def short_conv(x, taps, *, seq_info, state, max_tokens: int, act: int = 1):
     if K > 1 and (state is None or state.dtype != torch.float32 or state.shape[1:] != (C, K - 1) or not state[0].is_contiguous()):
         raise RuntimeError("short_conv: state must be float32 [slots, C, K - 1]")
     y = torch.empty((T, C), dtype=x.dtype, device=x.device)
-    _check(library().tlb_short_conv(_ptr(x), x.stride(0), _ptr(taps), C, K, int(act), _ptr(seq_info), seq_info.shape[0], max(1, int(max_tokens)),
+    _check(library().tlb_short_conv(_ptr(x), x.stride(0), _ptr(taps), _ptr(bias), int(bool(add_input)), C, K, int(act), _ptr(seq_info), seq_info.shape[0], max(1, int(max_tokens)),
                                     _ptr(state) if K > 1 else None, state.stride(0) if K > 1 else 0, state.shape[0] if K > 1 else 0, _ptr(y),
                                     _code(x.dtype), _stream(x)))
     return y
 
 
 def act_rows(x: torch.Tensor, act: int) -> torch.Tensor:
-    """``act(x)`` elementwise (``ACT_SILU``, ``ACT_GELU_TANH``, ``ACT_RELU_SQUARED``)."""
+    """``act(x)`` elementwise (``ACT_SILU``, ``ACT_GELU_TANH``, ``ACT_RELU_SQUARED``, ``ACT_TANH``)."""
     _gpu("act_rows", x)
     _contig("act_rows", x)
     out = torch.empty_like(x)
@@ -645,4 +692,47 @@ def argmax_rows(logits: torch.Tensor) -> torch.Tensor:
         raise RuntimeError("argmax_rows: expected float32 [rows, vocab]")
     out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
     _check(library().tlb_argmax_rows(_ptr(logits), _ptr(out), logits.shape[0], logits.shape[1], _stream(logits)))
+    return out
+
+
+def streams_step(xs, *, x0=None, y=None, y_bias=None, write=None, read=None, eps: float = 0.0, dtype=None):
+    """Residual streams ``xs [rows, n, dim]`` fp32 (in place) around a sublayer.  ``write`` (fp32 ``[n * n + n]``: the mixing
+    matrix indexed [from, to], then the output weights) with the sublayer's output ``y [rows, dim]`` fp32 (+ ``y_bias [dim]``):
+    ``x_t <- sum_s mix[s, t] x_s + out[t] (y + y_bias)``.  ``read`` (fp32 ``[n + 1]``: the input weights, then the norm's one
+    weight): returns ``rms_norm(sum_s in[s] x_s) * g`` rounded to ``dtype``.  ``x0 [rows, dim]`` fp32: every stream starts as
+    that row."""
+    _gpu("streams_step", xs, x0, y, y_bias, write, read)
+    _contig("streams_step", xs, x0, y, y_bias, write, read)
+    rows, n, dim = xs.shape
+    if xs.dtype != torch.float32 or any(t is not None and (t.dtype != torch.float32 or t.shape != (rows, dim)) for t in (x0, y)):
+        raise RuntimeError("streams_step: streams [rows, n, dim], x0 and y [rows, dim] must be float32")
+    if (write is not None and (y is None or write.dtype != torch.float32 or write.numel() != n * n + n)) or (read is not None and (read.dtype != torch.float32 or read.numel() != n + 1)):
+        raise RuntimeError("streams_step: write must be float32 [n * n + n] (with y), read float32 [n + 1]")
+    if y_bias is not None:
+        dtype = y_bias.dtype
+    h = None
+    if read is not None:
+        if dtype is None:
+            raise RuntimeError("streams_step: name the dtype of the norm's output")
+        h = torch.empty((rows, dim), dtype=dtype, device=xs.device)
+    _check(library().tlb_streams_step(_ptr(xs), _ptr(x0), _ptr(y), _ptr(y_bias), _ptr(write), _ptr(read), float(eps), _ptr(h), rows, n, dim,
+                                      _code(dtype if dtype is not None else torch.float32), _stream(xs)))
+    return h
+
+
+def shift_mix(h, mu, *, seq_info, state, max_tokens: int):
+    """Token shift: ``out[i, t] = h[t] + (h[t-1] - h[t]) * mu[i]`` along every sequence; ``h [T, dim]`` (unit inner stride),
+    ``mu [n, dim]`` (n <= 8), ``state [slots, dim]`` fp32 (a view whose slots may be further apart): the row before the step's
+    first token, replaced by the step's last one; zero before position 0 -> ``[n, T, dim]``."""
+    _gpu("shift_mix", h, mu, seq_info, state)
+    _contig("shift_mix", mu, seq_info)
+    T, dim = h.shape
+    n = mu.shape[0]
+    if mu.shape != (n, dim) or mu.dtype != h.dtype or h.stride(1) != 1 or n > 8:
+        raise RuntimeError("shift_mix: mu must be [n <= 8, dim] of h's dtype")
+    if state.dtype != torch.float32 or state.shape[1:] != (dim,) or state.stride(1) != 1:
+        raise RuntimeError("shift_mix: state must be float32 [slots, dim]")
+    out = torch.empty((n, T, dim), dtype=h.dtype, device=h.device)
+    _check(library().tlb_shift_mix(_ptr(h), h.stride(0), _ptr(mu), n, dim, _ptr(seq_info), seq_info.shape[0], max(1, int(max_tokens)), _ptr(state),
+                                   state.stride(0), state.shape[0], _ptr(out), T * dim, _code(h.dtype), _stream(h)))
     return out

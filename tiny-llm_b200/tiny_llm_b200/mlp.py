@@ -14,7 +14,7 @@ import torch
 
 from .basics import linear, linear_wide
 
-ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "relu_squared": 2}
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "relu_squared": 2, "clamped_swish": 3}
 SCORINGS = {"softmax": 0, "sigmoid": 1, "softmax_all": 2}
 
 
@@ -31,16 +31,29 @@ class DenseMLP:
 
 
 class GatedMLP:
-    def __init__(self, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, act: str):
+    """``act="clamped_swish"`` (with ``limit`` and ``slope``): ``g = min(gate x, limit)``, ``u = clamp(up x, -limit, limit)``,
+    ``down(g sigmoid(slope g) (u + 1))``.  ``b_gate`` / ``b_up`` are added by the first product; ``b_down`` is kept for the
+    caller (``down_bias``), who adds it where the residual sum is made."""
+
+    def __init__(self, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, act: str, b_gate=None, b_up=None, b_down=None,
+                 limit: float = 0.0, slope: float = 1.0):
         self.w_gate_up = torch.cat([w_gate, w_up], dim=0).contiguous()  # [2 ff, D]: one product for both
         self.w_down = w_down.contiguous()
         self.act = ACTIVATIONS[act]
+        if (b_gate is None) != (b_up is None):
+            raise ValueError("gated feed-forward: biases on both first projections or on neither")
+        self.b_gate_up = None if b_gate is None else torch.cat([b_gate, b_up]).contiguous()
+        self.down_bias = None if b_down is None else b_down.contiguous()
+        self.limit, self.slope = float(limit), float(slope)
+        if act == "clamped_swish" and not self.limit > 0:
+            raise ValueError("gated feed-forward: the clamped activation needs a positive limit")
 
     def __call__(self, h: torch.Tensor, wide: bool = False) -> torch.Tensor:
         """``wide``: hand the down projection's fp32 accumulator back unrounded (when a norm reads it next)."""
         from extensions_b200.tiny_llm_ext_b200 import blocks
 
-        return (linear_wide if wide else linear)(blocks.gated_act(linear(h, self.w_gate_up), self.act), self.w_down)
+        first = linear(h, self.w_gate_up) if self.b_gate_up is None else torch.addmm(self.b_gate_up, h, self.w_gate_up.t())
+        return (linear_wide if wide else linear)(blocks.gated_act(first, self.act, self.limit, self.slope), self.w_down)
 
 
 class TopKRouter:

@@ -20,6 +20,7 @@ ARCHITECTURES = {
     "Voluzen": ("tiny_llm_b200.voluzen", "VoluzenModel"),
     "Bapovik": ("tiny_llm_b200.bapovik", "BapovikModel"),
     "Senurax": ("tiny_llm_b200.senurax", "SenuraxModel"),
+    "Norusun": ("tiny_llm_b200.norusun", "NorusunModel"),
 }
 
 

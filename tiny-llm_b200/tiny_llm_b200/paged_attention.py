@@ -6,6 +6,10 @@ norms of queries and keys (plain weights of size ``dim``, shared by the heads) a
 (``gate`` None = no gate).  With ``rot`` = ``{"dims", "base", "factor", "interleaved"}`` the first ``dims`` entries of every
 query and key head are rotated by the token's position (pairs ``(2i, 2i+1)`` or ``(i, i + dims/2)``, every frequency
 divided by ``factor``) before the keys are stored; without it the scores carry no positional term.
+``qk_norm="whole"``: each norm takes a token's whole query (key) projection as one vector, ahead of the split into heads and
+before any rotation, with weights of that size.  ``head_bias`` (one learned number per head): with ``sink`` the sink's term is
+``exp(head_bias[h])``; with ``weights="sigmoid"`` there is no softmax at all, a visible key weighs
+``sigmoid(score + head_bias[h])`` and nothing is normalised over the keys.
 
 The layer's input projections are made by the caller in one product (``FusedProjection``); the module takes the views
 ``q [T, H * dim]``, ``k [T, G * dim]``, ``v [T, G * vdim]`` and ``gate [T, H]`` (logits), stores keys and values in the
@@ -20,6 +24,7 @@ import torch
 from .basics import linear, linear_wide
 
 MASKS = {"causal": 0, "window": 1, "chunk": 2}
+WEIGHTS = {"softmax": 0, "sigmoid": 1}
 
 
 class FusedProjection:
@@ -48,7 +53,8 @@ class FusedProjection:
 
 class PagedGroupedAttention:
     def __init__(self, *, heads: int, kv_heads: int, dim: int, vdim: int, scale: float, mask: str, mask_size: int, w_o, softcap: float | None = None,
-                 sink: bool = False, q_norm=None, k_norm=None, eps: float = 1e-6, caches: bool = True, page_size: int = 64, rot: dict | None = None):
+                 sink: bool = False, q_norm=None, k_norm=None, eps: float = 1e-6, caches: bool = True, page_size: int = 64, rot: dict | None = None,
+                 qk_norm: str = "head", head_bias=None, weights: str = "softmax"):
         if heads % kv_heads:
             raise ValueError(f"{heads} query heads do not divide into {kv_heads} key/value heads")
         if mask not in MASKS or (mask != "causal" and int(mask_size) <= 0):
@@ -61,9 +67,19 @@ class PagedGroupedAttention:
         self.q_norm = None if q_norm is None else q_norm.contiguous()
         self.k_norm = None if k_norm is None else k_norm.contiguous()
         self.w_o = w_o.contiguous()
+        if qk_norm not in ("head", "whole") or weights not in WEIGHTS:
+            raise ValueError(f"attention: qk_norm={qk_norm!r}, weights={weights!r}")
+        self.whole_norm, self.weights = qk_norm == "whole", WEIGHTS[weights]
+        if self.whole_norm and (q_norm is None or q_norm.numel() != heads * dim or (k_norm is not None and k_norm.numel() != kv_heads * dim)):
+            raise ValueError("attention: norms over the whole projection take weights of heads x dim")
+        self.head_bias = None if head_bias is None else head_bias.detach().float().contiguous()  # scores and weights are fp32
+        if self.head_bias is not None and self.head_bias.numel() != heads:
+            raise ValueError("attention: one head_bias per head")
+        if self.weights == WEIGHTS["sigmoid"] and (sink or softcap):
+            raise ValueError("attention: sigmoid weights take no sink and no cap")
         self.rot = None
         if rot and int(rot.get("dims", 0)) > 0:
-            if q_norm is not None or k_norm is not None:
+            if (q_norm is not None or k_norm is not None) and not self.whole_norm:
                 raise ValueError("attention: rotation together with query / key norms is not built")
             self.rot = {"dims": int(rot["dims"]), "base": float(rot["base"]), "factor": float(rot.get("factor", 1.0)), "interleaved": bool(rot.get("interleaved", False))}
             if self.rot["dims"] % 2 or self.rot["dims"] > self.dim:
@@ -82,17 +98,23 @@ class PagedGroupedAttention:
 
         T, H, G = q.shape[0], self.heads, self.kv_heads
         q3 = q.unflatten(1, (H, self.dim))
+        q_norm, k_norm = self.q_norm, self.k_norm
+        if self.whole_norm:  # each projection as ONE row: normed in place before anything else touches it
+            blocks.kv_prepare(q.unflatten(1, (1, H * self.dim)), None, None, q_norm=q_norm, eps=self.eps)
+            if self.caches and k_norm is not None:
+                blocks.kv_prepare(k.unflatten(1, (1, G * self.dim)), None, None, q_norm=k_norm, eps=self.eps)
+            q_norm = k_norm = None
         if self.rot is not None:
             r = self.rot
             blocks.rope_rows(q, plan.tok_pos, heads=H, head_stride=self.dim, first=0, dims=r["dims"], base=r["base"], interleaved=r["interleaved"], factor=r["factor"])
             if self.caches:
                 blocks.rope_rows(k, plan.tok_pos, heads=G, head_stride=self.dim, first=0, dims=r["dims"], base=r["base"], interleaved=r["interleaved"], factor=r["factor"])
         if self.caches:
-            blocks.kv_prepare(q3, k.unflatten(1, (G, self.dim)), v.unflatten(1, (G, self.vdim)), q_norm=self.q_norm, k_norm=self.k_norm, eps=self.eps,
+            blocks.kv_prepare(q3, k.unflatten(1, (G, self.dim)), v.unflatten(1, (G, self.vdim)), q_norm=q_norm, k_norm=k_norm, eps=self.eps,
                               tok_pos=plan.tok_pos, tok_seq=plan.tok_seq, block_table=plan.block_table, slab=slab)
-        elif self.q_norm is not None:
-            blocks.kv_prepare(q3, None, None, q_norm=self.q_norm, eps=self.eps)
+        elif q_norm is not None:
+            blocks.kv_prepare(q3, None, None, q_norm=q_norm, eps=self.eps)
         o = blocks.paged_attention(q3, slab, plan.block_table, plan.tiles_for(self.tile_tokens), plan.tok_pos, kv_heads=G, dv=self.vdim, mask=self.mask,
                                    mask_size=self.mask_size, scale=self.scale, softcap=self.softcap, sink=self.sink, gate=gate, kernel=self.kernel,
-                                   max_context=getattr(plan, "max_context", 0))
+                                   max_context=getattr(plan, "max_context", 0), head_bias=self.head_bias, weights=self.weights)
         return linear_wide(o.view(T, H * self.vdim), self.w_o)  # fp32: a norm or the residual sum reads it unrounded
