@@ -127,11 +127,11 @@ def sink_softmax_attention(q, k, v, sink, *, scale, kind, size) -> torch.Tensor:
     for h in range(H):
         for i in range(T):
             js = [j for j in range(T) if visible(i, j, kind, size)]
-            s = torch.stack([(q[i, h] * k[j, h]).sum() * scale for j in js])
+            s = (k[js, h] @ q[i, h]) * scale
             m = torch.maximum(s.max(), sink[h])
             e = torch.exp(s - m)
             p = e / (e.sum() + torch.exp(sink[h] - m))
-            out[i, h] = sum(p[n] * v[j, h] for n, j in enumerate(js))
+            out[i, h] = p @ v[js, h]
     return out
 
 
@@ -157,9 +157,8 @@ def sigmoid_attention(q, k, v, bias, *, scale, kind, size) -> torch.Tensor:
     out = torch.zeros((T, H, v.shape[2]), dtype=q.dtype)
     for h in range(H):
         for i in range(T):
-            for j in range(T):
-                if visible(i, j, kind, size):
-                    out[i, h] += torch.sigmoid((q[i, h] * k[j, h]).sum() * scale + bias[h]) * v[j, h]
+            js = [j for j in range(T) if visible(i, j, kind, size)]
+            out[i, h] = torch.sigmoid((k[js, h] @ q[i, h]) * scale + bias[h]) @ v[js, h]
     return out
 
 

@@ -9,9 +9,10 @@ see checkpoint.py; there is no hub download here).
     python -m tiny_llm_b200.cli generate --synthetic voluzen:WCSM --prompt-ids 5,17,3 --max-new-tokens 8
     python -m tiny_llm_b200.cli generate --synthetic bapovik:APSP --prompt-ids 5,17,3 --max-new-tokens 8
     python -m tiny_llm_b200.cli generate --synthetic senurax:RdCmPm --prompt-ids 5,17,3 --max-new-tokens 8
+    python -m tiny_llm_b200.cli generate --synthetic norusun:LdPdWn --prompt-ids 5,17,3 --max-new-tokens 8
     python -m tiny_llm_b200.cli trace    --model DIR --dtype float32 --out DIR --max-tokens N < steps.jsonl   (trace_runner.py)
 
-A checkpoint whose config.json names its ``architecture`` (Voluzen, Bapovik, Senurax) is built by that design's class
+A checkpoint whose config.json names its ``architecture`` (Voluzen, Bapovik, Senurax, Norusun) is built by that design's class
 (``models.load_model``); such models take ``--dtype`` and batch with mixed prefill + decode steps.
 """
 
@@ -49,6 +50,12 @@ def _self_describing(args, device):
         count = len(pattern) // 2
         config = senurax_config(pattern=pattern, loop=(min(1, count - 1), count, 2))  # all layers but the first run twice
         return model_class("Senurax").from_checkpoint(config, synthetic_senurax(config, seed=0), device=device, dtype=dtype)
+    if args.synthetic and args.synthetic.startswith("norusun"):
+        from .models import model_class
+        from .synthetic import norusun_config, synthetic_norusun
+
+        config = norusun_config(pattern=args.synthetic.partition(":")[2] or "LdPdWnLd")
+        return model_class("Norusun").from_checkpoint(config, synthetic_norusun(config, seed=0), device=device, dtype=dtype)
     if args.model and "architecture" in json.loads((Path(args.model) / "config.json").read_text()):
         from .models import load_model
 
@@ -159,7 +166,7 @@ def main(argv=None) -> int:
         p = sub.add_parser(name)
         p.set_defaults(fn=fn)
         p.add_argument("--model", default=None, help="checkpoint directory (config.json + *.safetensors [+ tokenizer files])")
-        p.add_argument("--synthetic", default=None, help="random weights of a named shape (tiny, tiny-d128, qwen3-0.6b, qwen3-4b, voluzen[:LAYERS], bapovik[:LAYERS], senurax[:LAYERS]) instead of --model")
+        p.add_argument("--synthetic", default=None, help="random weights of a named shape (tiny, tiny-d128, qwen3-0.6b, qwen3-4b, voluzen[:LAYERS], bapovik[:LAYERS], senurax[:LAYERS], norusun[:LAYERS]) instead of --model")
         p.add_argument("--prompt", default="Give me a short introduction to large language models.")
         p.add_argument("--prompt-ids", default=None, help="comma-separated token ids (';' between requests for `batch`)")
         p.add_argument("--loader", choices=["week2", "week3"], default="week3")

@@ -455,3 +455,111 @@ def synthetic_senurax(config: dict, seed: int = 0, dtype=torch.bfloat16) -> dict
 
 
 save_senurax = save_voluzen
+
+
+# ---- Norusun (time-mix linear attention / latent attention with sinks / sigmoid attention beside a state-space mixer; norusun.py) ----
+def norusun_config(*, width=96, vocab=200, pattern="LdPdWnLd", streams=2, canon_taps=4, heads=4, kv_heads=2, dim=16, vdim=24, chunk=24, rot_dims=16,
+                   rot_base=20000.0, scale=None, lat_heads=3, lat_dim=16, lat_rot=8, lat_vdim=16, kv_rank=24, q_rank=40, window=20, lat_base=10000.0,
+                   lat_scale=None, ss_heads=4, ss_vdim=16, ss_state=16, ss_groups=2, ss_norm_groups=2, ss_taps=4, wkv_heads=3, wkv_dim=32, ff=160,
+                   limit=3.0, eps=1e-6) -> dict:
+    """A config.json for a stack spelled by ``pattern``, two letters a layer: the mixer (``W`` time-mix linear attention,
+    ``L`` latent attention, ``P`` chunked sigmoid attention beside a state-space mixer) and the feed-forward (``d`` dense,
+    ``n`` none).  ``streams`` 0 = no residual streams, ``canon_taps`` 0 = no input convolution.  ``width`` must equal
+    ``wkv_heads * wkv_dim`` when the stack has a ``W`` layer."""
+    if len(pattern) % 2:
+        raise ValueError("the pattern is pairs of letters: mixer, feed-forward")
+    layers = []
+    for mixer_letter, ff_letter in zip(pattern[0::2], pattern[1::2]):
+        if ff_letter not in "dn":
+            raise ValueError(f"unknown feed-forward letter {ff_letter!r}")
+        mlp = {"kind": "dense", "ff": ff, "limit": limit} if ff_letter == "d" else None
+        if mixer_letter == "W":
+            layers.append({"type": "wkv", "mixer": {"heads": wkv_heads, "dim": wkv_dim}, "mlp": mlp})
+        elif mixer_letter == "L":
+            mixer = {"heads": lat_heads, "dim": lat_dim, "rot_dim": lat_rot, "vdim": lat_vdim, "kv_rank": kv_rank, "q_rank": q_rank, "mask": {"size": window},
+                     "rot": {"base": lat_base, "dims": lat_rot}, "scale": float(lat_scale if lat_scale is not None else (lat_dim + lat_rot) ** -0.5)}
+            layers.append({"type": "latent_attention", "mixer": mixer, "mlp": mlp})
+        elif mixer_letter == "P":
+            left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "mask": {"size": chunk}, "rot": {"base": rot_base, "dims": rot_dims},
+                    "scale": float(scale if scale is not None else dim ** -0.5)}
+            right = {"conv": ss_taps, "groups": ss_groups, "heads": ss_heads, "norm_groups": ss_norm_groups, "state": ss_state, "vdim": ss_vdim}
+            layers.append({"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": mlp})
+        else:
+            raise ValueError(f"unknown mixer letter {mixer_letter!r}")
+    config = {"architecture": "Norusun", "vocab": vocab, "width": width, "norm": {"eps": eps}, "layers": layers}
+    if streams:
+        config["streams"] = streams
+    if canon_taps:
+        config["canon"] = {"taps": canon_taps}
+    return config
+
+
+def synthetic_norusun(config: dict, seed: int = 0, dtype=torch.bfloat16) -> dict:
+    """Random tensors for ``config`` under the checkpoint's names (CPU, seeded)."""
+    gen = torch.Generator().manual_seed(seed)
+    D = config["width"]
+    n = int(config.get("streams") or 0)
+    taps = int((config.get("canon") or {}).get("taps") or 0)
+
+    def mat(out_dim, in_dim, gain=1.0):
+        return (torch.randn(out_dim, in_dim, generator=gen) * (gain / in_dim**0.5)).to(dtype)
+
+    def vec(count, centre, spread):
+        return (centre + spread * torch.randn(count, generator=gen)).to(dtype)
+
+    def scalar(centre, spread):
+        return vec(1, centre, spread).reshape(())
+
+    tensors = {"embed": torch.randn(config["vocab"], D, generator=gen).to(dtype), "final.norm": scalar(1.0, 0.1), "head": mat(config["vocab"], D)}
+
+    def sublayer(p, q):
+        tensors[p + f"norm{q}"] = scalar(1.0, 0.1)
+        if n:
+            tensors[p + f"hc{q}.in"], tensors[p + f"hc{q}.out"] = vec(n, 1.0 / n, 0.2), vec(n, 1.0, 0.3)
+            tensors[p + f"hc{q}.mix"] = (torch.eye(n) + 0.2 * torch.randn(n, n, generator=gen)).to(dtype)
+
+    for i, layer in enumerate(config["layers"]):
+        m, p = layer["mixer"], f"l{i}."
+        sublayer(p, 1)
+        if taps:
+            tensors[p + "canon1"] = (0.3 * torch.randn(D, taps, generator=gen)).to(dtype)
+        x = p + "mix."
+        if layer["type"] == "wkv":
+            hd = m["heads"] * m["dim"]
+            low = max(4, D // 16)
+            for name in "rkvgw":
+                tensors[x + "mu." + name] = torch.rand(D, generator=gen).to(dtype)
+            tensors[x + "r"], tensors[x + "k"], tensors[x + "v"], tensors[x + "g"] = mat(hd, D), mat(hd, D), mat(hd, D), mat(hd, D)
+            tensors[x + "w1"], tensors[x + "w2"], tensors[x + "w0"] = mat(low, D), mat(hd, low, 2.0), vec(hd, -1.5, 1.0)
+            tensors[x + "u"] = (0.5 * torch.randn(m["heads"], m["dim"], generator=gen)).to(dtype)
+            tensors[x + "norm"], tensors[x + "o"] = vec(hd, 1.0, 0.2), mat(D, hd)
+        elif layer["type"] == "latent_attention":
+            H, dn, dr, dv, rank, qr = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"], m["q_rank"]
+            tensors[x + "dq"], tensors[x + "dq.norm"], tensors[x + "uq"] = mat(qr, D), vec(qr, 1.0, 0.2), mat(H * (dn + dr), qr, 2.0)
+            tensors[x + "dkv"], tensors[x + "dkv.norm"] = mat(rank + dr, D, 2.0), vec(rank, 1.0, 0.2)
+            tensors[x + "uk"], tensors[x + "uv"], tensors[x + "o"] = mat(H * dn, rank, 2.0), mat(H * dv, rank), mat(D, H * dv)
+            tensors[x + "sink"] = vec(H, 0.0, 1.0)
+        else:
+            a, r, lp, rp = m["left"], m["right"], x + "left.", x + "right."
+            H, G, dk, dv = a["heads"], a["kv_heads"], a["dim"], a["vdim"]
+            tensors[lp + "q"], tensors[lp + "k"], tensors[lp + "v"], tensors[lp + "o"] = mat(H * dk, D, 2.0), mat(G * dk, D, 2.0), mat(G * dv, D), mat(D, H * dv)
+            tensors[lp + "q.norm"], tensors[lp + "k.norm"], tensors[lp + "pb"] = vec(H * dk, 1.0, 0.2), vec(G * dk, 1.0, 0.2), vec(H, -2.0, 1.0)
+            SH, P, N, SG, K = r["heads"], r["vdim"], r["state"], r["groups"], r["conv"]
+            inner, channels = SH * P, SH * P + 2 * SG * N
+            tensors[rp + "in"] = mat(2 * inner + 2 * SG * N + SH, D, 1.5)
+            tensors[rp + "conv"] = (torch.randn(channels, K, generator=gen) * 0.4 + torch.eye(K)[K - 1]).to(dtype)
+            tensors[rp + "conv.b"] = vec(channels, 0.0, 0.1)
+            tensors[rp + "dt_bias"], tensors[rp + "A_log"], tensors[rp + "D"] = vec(SH, -1.0, 1.0), vec(SH, -0.5, 0.7), vec(SH, 1.0, 0.3)
+            tensors[rp + "norm"], tensors[rp + "o"] = vec(inner, 1.0, 0.2), mat(D, inner)
+            tensors[lp + "out"], tensors[rp + "out"] = vec(D, 1.0, 0.2), vec(D, 1.0, 0.2)
+        mlp = layer.get("mlp")
+        if mlp:
+            sublayer(p, 2)
+            f = mlp["ff"]
+            tensors[p + "mlp.gate"], tensors[p + "mlp.gate.b"] = mat(f, D, 2.0), vec(f, 0.0, 0.5)
+            tensors[p + "mlp.up"], tensors[p + "mlp.up.b"] = mat(f, D, 2.0), vec(f, 0.0, 0.5)
+            tensors[p + "mlp.down"], tensors[p + "mlp.down.b"] = mat(D, f), vec(D, 0.0, 0.2)
+    return tensors
+
+
+save_norusun = save_voluzen
