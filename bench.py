@@ -38,6 +38,9 @@ Numbers on the JSON line (decode):
   --workload senurax  (not a BASELINE config) the Senurax design - retention, gated delta rule and rotated attention mixers,
                       looped layers, experts with identity experts - at a few real-layer sizes beside Bapovik of equal size, and its
                       kernels against their rooflines.
+  --workload norusun  (not a BASELINE config) the Norusun design - residual streams, time-mix linear attention, latent attention with
+                      learned sinks, chunked sigmoid attention beside a state-space mixer - at two real-layer sizes beside Senurax of
+                      equal size, and its kernels against their rooflines.
   --workload bapovik  (not a BASELINE config) the Bapovik design - windowed / chunked attention beside a recurrent mixer, experts,
             bf16 weights - at two sizes beside Voluzen of equal size, and the design's kernels alone against the measured peaks
   cpu_baseline  the reference's CPU path (oracle.model: dense bf16 weights, readable operators) on the
@@ -1408,6 +1411,240 @@ def run_senurax(args) -> None:
                       "dtype": "bf16 (unquantised weights in both)", "data": "synthetic (random weights, random prompts)",
                       "steps": steps, "warmup": max(args.warmup, 3), "peaks": measured_peaks(), "clocks": clocks, "sizes": results}), flush=True)
 
+# ------------------------------------------------------------------ workload: norusun (residual streams, time-mix / latent / sigmoid attention beside a state-space mixer; beside Senurax of equal size)
+NORUSUN_SIZES = {
+    # four layers at sizes that resemble real models of this kind: two latent-attention layers (query latent, window, learned sinks),
+    # a parallel layer (chunked sigmoid attention beside a state-space mixer) and a time-mix layer without a feed-forward, two residual
+    # streams, a four-tap input convolution.  The Senurax arm (the framework's closest model: pre-norm, dense feed-forwards, attention
+    # beside recurrent mixers with short convolutions, the same ragged step, page pool and state slots) has the same width, depth, head
+    # counts and head sizes; its ungated feed-forward has 3/2 of the inner width, so that it has the same number of weights.
+    "w1024": dict(width=1024, vocab=32768, pattern="LdPdWnLd", streams=2, canon_taps=4, heads=8, kv_heads=2, dim=128, vdim=128, chunk=1024, rot_dims=128,
+                  lat_heads=8, lat_dim=64, lat_rot=32, lat_vdim=64, kv_rank=256, q_rank=384, window=512, ss_heads=16, ss_vdim=64, ss_state=64, ss_groups=2,
+                  ss_norm_groups=2, ss_taps=4, wkv_heads=16, wkv_dim=64, ff=2816, limit=7.0),
+    "w2048": dict(width=2048, vocab=32768, pattern="LdPdWnLd", streams=2, canon_taps=4, heads=16, kv_heads=4, dim=128, vdim=128, chunk=2048, rot_dims=128,
+                  lat_heads=16, lat_dim=128, lat_rot=64, lat_vdim=128, kv_rank=512, q_rank=768, window=1024, ss_heads=32, ss_vdim=64, ss_state=128, ss_groups=4,
+                  ss_norm_groups=4, ss_taps=4, wkv_heads=32, wkv_dim=64, ff=5632, limit=7.0),
+}
+
+
+def _norusun_kernels(cfg: dict, device, prompt: int, batch: int, context: int) -> dict:
+    """The kernels the design added or extended, alone at this size, CUDA-event timed after warm-up, each against the roofline
+    of its kind (measured copy bandwidth for scans and row kernels, measured cuBLAS bf16 burst for contractions); between
+    repetitions a 256 MB buffer is rewritten to flush L2."""
+    from extensions_b200.tiny_llm_ext_b200 import blocks
+
+    peaks = measured_peaks()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    bf = torch.bfloat16
+
+    def timed(fn, reps=5):
+        for _ in range(3):
+            fn()
+        best = []
+        for _ in range(reps):
+            flush.fill_(1)
+            best.append(cuda_time_ms(fn))
+        return statistics.median(best)
+
+    def stream(nbytes, ms, **more):
+        return dict(more, ms=round(ms, 4), gbs=round(nbytes / ms / 1e6, 1), of_measured_hbm=round(nbytes / ms / 1e6 / peaks["hbm_gbs"], 4))
+
+    def seqs_info(tokens_per_seq, seqs, start):
+        return torch.tensor([(s * tokens_per_seq, tokens_per_seq, start, s) for s in range(seqs)], dtype=torch.int32, device=device)
+
+    out = {}
+    D, n, K = cfg["width"], cfg["streams"], cfg["canon_taps"]
+    rows = 32768
+    xs, y = torch.randn((rows, n, D), device=device), torch.randn((rows, D), device=device)
+    write = torch.cat([torch.eye(n).reshape(-1), torch.ones(n)]).to(device)
+    read = torch.cat([torch.ones(n) / n, torch.ones(1)]).to(device)
+    ms = timed(lambda: blocks.streams_step(xs, y=y, write=write, read=read, eps=1e-6, dtype=bf))
+    out["streams_step"] = stream(rows * D * (2 * n * 4 + 4 + 2), ms, rows=rows, streams=n)
+    h = torch.randn((rows, D), device=device).to(bf)
+    taps = torch.randn((D, K), device=device).to(bf)
+    hist = torch.zeros((batch, D, K - 1), device=device)
+    ms = timed(lambda: blocks.short_conv(h, taps, seq_info=seqs_info(rows, 1, 0), state=hist, max_tokens=rows, act=0, add_input=True))
+    out["input_conv_prefill"] = stream(rows * D * 2 * 2, ms, tokens=rows, channels=D)
+    ms = timed(lambda: blocks.short_conv(h[:batch], taps, seq_info=seqs_info(1, batch, context), state=hist, max_tokens=1, act=0, add_input=True))
+    out["input_conv_decode"] = stream(batch * D * (2 * 2 + (K - 1) * 4 * 2), ms, batch=batch)
+    mu, shift = torch.rand((5, D), device=device).to(bf), torch.zeros((batch, D), device=device)
+    ms = timed(lambda: blocks.shift_mix(h, mu, seq_info=seqs_info(rows, 1, 0), state=shift, max_tokens=rows))
+    out["shift_mix_prefill"] = stream(rows * D * 2 * 6, ms, tokens=rows)
+
+    WH, wd = cfg["wkv_heads"], cfg["wkv_dim"]
+
+    def wkv(tokens_per_seq, seqs, start):
+        T = tokens_per_seq * seqs
+        q, k, v = (torch.randn((T, WH, wd), device=device).to(bf) for _ in range(3))
+        z, zb, bonus = torch.randn((T, WH * wd), device=device), torch.zeros(WH * wd, device=device).to(bf), torch.randn((WH, wd), device=device).to(bf)
+        state = torch.zeros((seqs, WH, wd, wd), device=device)
+        info = seqs_info(tokens_per_seq, seqs, start)
+        return timed(lambda: blocks.decay_scan(q, k, v, z, zb, q_scale=1.0, seq_info=info, state=state, max_tokens=tokens_per_seq,
+                                               decay_kind=blocks.DECAY_DOUBLE_EXP, bonus=bonus))
+
+    ms = wkv(prompt, 1, 0)
+    out["wkv_scan_prefill"] = stream(prompt * WH * wd * (3 * 2 + 4 + 4), ms, tokens=prompt, gflops=round(5.0 * prompt * WH * wd * wd / ms / 1e6, 1),
+                                     note="decay_scan with a double-exponential decay per channel and the read-out before the update; three launches over 64-token segments")
+    ms = wkv(1, batch, context)
+    out["wkv_scan_decode"] = stream(batch * WH * wd * wd * 4 * 2, ms, batch=batch)
+
+    SH, P, N, G, SK = cfg["ss_heads"], cfg["ss_vdim"], cfg["ss_state"], cfg["ss_groups"], cfg["ss_taps"]
+
+    def ssm(tokens_per_seq, seqs, start):
+        T = tokens_per_seq * seqs
+        x, B, C = torch.randn((T, SH, P), device=device).to(bf), torch.randn((T, G, N), device=device).to(bf), torch.randn((T, G, N), device=device).to(bf)
+        z, zb, a_log, skip = torch.randn((T, SH), device=device), torch.zeros(SH, device=device).to(bf), torch.zeros(SH, device=device).to(bf), torch.ones(SH, device=device).to(bf)
+        state = torch.zeros((seqs, SH, N, P), device=device)
+        info = seqs_info(tokens_per_seq, seqs, start)
+        return timed(lambda: blocks.decay_scan(C, B, x, z, zb, q_scale=1.0, seq_info=info, state=state, max_tokens=tokens_per_seq, decay_kind=blocks.DECAY_STEP,
+                                               a_log=a_log, skip=skip))
+
+    ms = ssm(prompt, 1, 0)
+    out["state_space_scan_prefill"] = stream(prompt * (SH * P * (2 + 4) + 2 * G * N * 2 + SH * 4), ms, tokens=prompt, gflops=round(4.0 * prompt * SH * N * P / ms / 1e6, 1))
+    ms = ssm(1, batch, context)
+    out["state_space_scan_decode"] = stream(batch * SH * N * P * 4 * 2, ms, batch=batch)
+    channels = SH * P + 2 * G * N
+    xw = torch.randn((rows, channels + 64), device=device).to(bf)[:, 32 : 32 + channels]  # columns of a wider product, as in the model
+    ctaps, cb = torch.randn((channels, SK), device=device).to(bf), torch.zeros(channels, device=device).to(bf)
+    chist = torch.zeros((1, channels, SK - 1), device=device)
+    ms = timed(lambda: blocks.short_conv(xw, ctaps, seq_info=seqs_info(rows, 1, 0), state=chist, max_tokens=rows, act=1, bias=cb))
+    out["state_space_conv_prefill"] = stream(rows * channels * 2 * 2, ms, tokens=rows, channels=channels)
+    o32, gate, nw = torch.randn((rows, SH * P), device=device), torch.randn((rows, SH * P), device=device).to(bf), torch.ones(SH * P, device=device).to(bf)
+    parts = cfg["ss_norm_groups"]
+    ms = timed(lambda: blocks.head_norm_gate(o32.view(rows, parts, -1), nw, 1e-6, gate, act=1, gate_first=True))
+    out["gate_then_group_norm"] = stream(rows * SH * P * (4 + 2 + 2), ms, rows=rows)
+
+    page = 64
+    LH, rank, rot, window = cfg["lat_heads"], cfg["kv_rank"], cfg["lat_rot"], cfg["window"]
+    lkernel, ltile = blocks.attention_kernel(bf, LH, rank, rot, page)
+    sink = torch.randn(LH, device=device)
+
+    def latent(tokens_per_seq, seqs, ctx):
+        pages_per = -(-ctx // page)
+        slab = torch.randn((seqs * pages_per, page, rank + rot), device=device).to(bf)
+        table = torch.arange(seqs * pages_per, dtype=torch.int32, device=device).view(seqs, pages_per)
+        T = tokens_per_seq * seqs
+        pos = torch.cat([torch.arange(ctx - tokens_per_seq, ctx, dtype=torch.int32) for _ in range(seqs)]).to(device)
+        tiles = torch.tensor([(s * tokens_per_seq + f, min(ltile, tokens_per_seq - f), s) for s in range(seqs) for f in range(0, tokens_per_seq, ltile)],
+                             dtype=torch.int32, device=device)
+        ql, qr = torch.randn((T, LH, rank), device=device).to(bf), torch.randn((T, LH, rot), device=device).to(bf)
+        o = torch.empty((T, LH, rank), dtype=bf, device=device)
+        return timed(lambda: blocks.latent_attention(ql, qr, slab, table, tiles, pos, window=window, scale=0.1, out=o, kernel=lkernel, max_context=ctx, sink=sink))
+
+    ms = latent(prompt, 1, prompt)
+    seen = sum(min(p + 1, window) for p in range(prompt))
+    flops = 2.0 * LH * (2 * rank + rot) * seen
+    out["latent_window_sink_attention_prefill"] = {"kernel": lkernel, "tokens": prompt, "window": window, "ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1),
+                                                   "of_measured_bf16_burst": round(flops / ms / 1e9 / peaks["bf16_tflops"], 4)}
+    ms = latent(1, batch, context)
+    out["latent_window_sink_attention_decode"] = stream(batch * min(context, window) * (rank + rot) * 2, ms, kernel=lkernel, batch=batch, context=context)
+
+    AH, AG, ak, av, chunk = cfg["heads"], cfg["kv_heads"], cfg["dim"], cfg["vdim"], cfg["chunk"]
+    kernel, tile = blocks.paged_attention_kernel(bf, AH, AG, ak, av, page)
+    pb = torch.full((AH,), -3.0, device=device)
+
+    def attention(tokens_per_seq, seqs, ctx):
+        pages_per = -(-ctx // page)
+        slab = torch.randn((seqs * pages_per, page, AG * (ak + av)), dtype=torch.float32, device=device).to(bf)
+        table = torch.arange(seqs * pages_per, dtype=torch.int32, device=device).view(seqs, pages_per)
+        T = tokens_per_seq * seqs
+        pos = torch.cat([torch.arange(ctx - tokens_per_seq, ctx, dtype=torch.int32) for _ in range(seqs)]).to(device)
+        tiles = torch.tensor([(s * tokens_per_seq + f, min(tile, tokens_per_seq - f), s) for s in range(seqs) for f in range(0, tokens_per_seq, tile)],
+                             dtype=torch.int32, device=device)
+        q = torch.randn((T, AH, ak), dtype=torch.float32, device=device).to(bf)
+        o = torch.empty((T, AH, av), dtype=bf, device=device)
+        return timed(lambda: blocks.paged_attention(q, slab, table, tiles, pos, kv_heads=AG, dv=av, mask=blocks.MASK_CHUNK, mask_size=chunk, scale=ak ** -0.5,
+                                                    out=o, kernel=kernel, max_context=ctx, head_bias=pb, weights=blocks.WEIGHTS_SIGMOID))
+
+    ms = attention(prompt, 1, prompt)
+    seen = sum(p % chunk + 1 for p in range(prompt))
+    flops = 2.0 * AH * (ak + av) * seen
+    out["chunk_sigmoid_attention_prefill"] = {"kernel": kernel, "tokens": prompt, "chunk": chunk, "ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1),
+                                              "of_measured_bf16_burst": round(flops / ms / 1e9 / peaks["bf16_tflops"], 4)}
+    ms = attention(1, batch, context)
+    out["chunk_sigmoid_attention_decode"] = stream(batch * ((context - 1) % chunk + 1) * AG * (ak + av) * 2, ms, kernel=kernel, batch=batch, context=context)
+    q = torch.randn((rows, AH * ak), device=device).to(bf)
+    qw = torch.ones(AH * ak, device=device).to(bf)
+    ms = timed(lambda: blocks.kv_prepare(q.unflatten(1, (1, AH * ak)), None, None, q_norm=qw, eps=1e-6))
+    out["whole_projection_norm"] = stream(rows * AH * ak * 2 * 2, ms, rows=rows)
+    ff = cfg["ff"]
+    gu = torch.randn((rows // 4, 2 * ff), device=device).to(bf)
+    ms = timed(lambda: blocks.gated_act(gu, blocks.ACT_CLAMPED_SWISH, cfg["limit"], 1.702))
+    out["clamped_gate"] = stream(rows // 4 * ff * 3 * 2, ms, rows=rows // 4)
+    return out
+
+
+def _measure_ragged(model, vocab: int, prompt: int, batch: int, context: int, steps: int, warmup: int) -> dict:
+    """Prefill of one prompt and decode steps of ``batch`` requests at ``context`` through the model's own ragged step."""
+    from tiny_llm_b200.batch import greedy_tokens
+    from tiny_llm_b200.ragged import RaggedEntry
+
+    ids = synthetic_prompt(1, prompt, vocab)
+
+    def prefill_once():
+        cache = model.create_kv_cache()
+        model.forward_ragged([RaggedEntry(ids, cache)])
+        cache[0].release()
+
+    for _ in range(warmup):
+        prefill_once()
+    pre_ms = statistics.median(cuda_time_ms(prefill_once) for _ in range(5))
+    caches = [model.create_kv_cache() for _ in range(batch)]
+    for b, cache in enumerate(caches):
+        model.forward_ragged([RaggedEntry(synthetic_prompt(10 + b, context, vocab), cache)])
+    tokens = [1] * batch
+
+    def decode_step():
+        nonlocal tokens
+        logits = model.forward_ragged([RaggedEntry([t], c) for t, c in zip(tokens, caches)])
+        tokens = greedy_tokens(logits).tolist()  # the device -> host read a serving step makes
+
+    for _ in range(warmup):
+        decode_step()
+    torch.cuda.synchronize()
+    dec_ms = cuda_time_ms(lambda: [decode_step() for _ in range(steps)]) / steps
+    for cache in caches:
+        cache[0].release()
+    return {"prefill_ms": round(pre_ms, 3), "prefill_tok_s": round(prompt / pre_ms * 1e3, 1), "decode_ms_per_step": round(dec_ms, 3),
+            "decode_tok_s": round(batch / dec_ms * 1e3, 1)}
+
+
+def run_norusun(args) -> None:
+    """Prefill and decode throughput of the Norusun design at NORUSUN_SIZES beside Senurax (the framework's closest model) of
+    equal size, through the same ragged step; and the design's kernels against their rooflines.  One JSON line; random
+    weights, random prompts."""
+    from tiny_llm_b200.models import model_class
+    from tiny_llm_b200.synthetic import norusun_config, senurax_config, synthetic_norusun, synthetic_senurax
+
+    device = torch.device("cuda:0")
+    prompt, batch, context, steps = args.prompt_len or 2048, 16, 1024, max(args.steps or 16, 4)
+    warmup = max(args.warmup, 3)
+    sampler = ClockSampler(0)
+    sampler.start()
+    results = []
+    for name, size in NORUSUN_SIZES.items():
+        config = norusun_config(**size)
+        model = model_class("Norusun").from_checkpoint(config, synthetic_norusun(config, seed=0), device=device, dtype=torch.bfloat16)
+        entry = {"size": name, "config": dict(size), "prompt_tokens": prompt, "decode_batch": batch, "decode_context": context,
+                 "norusun": _measure_ragged(model, size["vocab"], prompt, batch, context, steps, warmup)}
+        entry["kernels"] = _norusun_kernels(size, device, prompt, batch, context)
+        del model
+        torch.cuda.empty_cache()
+        ssize = dict(width=size["width"], vocab=size["vocab"], pattern="PdPdRnPd", loop=None, heads=size["heads"], kv_heads=size["kv_heads"], dim=size["dim"],
+                     vdim=size["vdim"], rot_dims=size["rot_dims"], rot_factor=1.0, rec_heads=size["ss_heads"], rec_key_heads=size["ss_groups"],
+                     rec_dim=size["ss_state"], rec_vdim=size["ss_vdim"], taps=size["ss_taps"], ret_heads=size["wkv_heads"], ret_dim=size["wkv_dim"],
+                     ret_vdim=size["wkv_dim"], ret_rot_dims=size["wkv_dim"], ff=size["ff"] * 3 // 2, softcap=0.0)
+        sconfig = senurax_config(**ssize)
+        other = model_class("Senurax").from_checkpoint(sconfig, synthetic_senurax(sconfig, seed=0), device=device, dtype=torch.bfloat16)
+        entry["senurax_equal_size"] = dict(_measure_ragged(other, size["vocab"], prompt, batch, context, steps, warmup), config=ssize)
+        del other
+        torch.cuda.empty_cache()
+        results.append(entry)
+    clocks = sampler.stop()
+    print(json.dumps({"workload": "norusun", "metric": "Norusun prefill / decode tok/s beside Senurax of equal size", "unit": UNIT, "n_gpus": 1,
+                      "dtype": "bf16 (unquantised weights in both)", "data": "synthetic (random weights, random prompts)",
+                      "steps": steps, "warmup": warmup, "peaks": measured_peaks(), "clocks": clocks, "sizes": results}), flush=True)
+
 
 def main() -> None:
     ap = argparse.ArgumentParser()
@@ -1415,7 +1652,7 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", choices=sorted(METRICS) + ["voluzen", "bapovik", "senurax"], default="decode")
+    ap.add_argument("--workload", choices=sorted(METRICS) + ["voluzen", "bapovik", "senurax", "norusun"], default="decode")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the sweeps / secondary measurements under `extra`")
     ap.add_argument("--requests", type=int, default=0, help="serve/serve8k: total requests over all ranks")
@@ -1431,6 +1668,8 @@ def main() -> None:
         run_bapovik(args)
     elif args.workload == "senurax":
         run_senurax(args)
+    elif args.workload == "norusun":
+        run_norusun(args)
     elif args.impl == "reference":
         run_reference(args)
     elif args.workload == "decode":

@@ -164,7 +164,18 @@ kv_prepare_kernel(T *q, long long q_token, long long q_head, int heads, const T 
                   const int32_t *__restrict__ block_table, int max_pages, int num_pages, int page_size, T *__restrict__ slab) {
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-    if (q != nullptr && q_norm != nullptr) {
+    if (q != nullptr && q_norm != nullptr && heads == 1) {  // one long row (a norm over a whole projection): the CTA shares it
+        __shared__ float scratch[33];
+        T *row = q + (size_t)t * q_token;
+        float ss = 0.f;
+        for (int d = threadIdx.x; d < dk; d += blockDim.x) {
+            float x = to_f(row[d]);
+            ss += x * x;
+        }
+        ss = block_sum(ss, scratch);
+        float inv = 1.0f / sqrtf(ss / (float)dk + eps);
+        for (int d = threadIdx.x; d < dk; d += blockDim.x) row[d] = from_f<T>(to_f(row[d]) * inv * to_f(q_norm[d]));
+    } else if (q != nullptr && q_norm != nullptr) {
         for (int hd = warp; hd < heads; hd += warps) {
             T *row = q + (size_t)t * q_token + (size_t)hd * q_head;
             float ss = 0.f;
