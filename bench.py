@@ -1563,10 +1563,14 @@ def _norusun_kernels(cfg: dict, device, prompt: int, batch: int, context: int) -
                                               "of_measured_bf16_burst": round(flops / ms / 1e9 / peaks["bf16_tflops"], 4)}
     ms = attention(1, batch, context)
     out["chunk_sigmoid_attention_decode"] = stream(batch * ((context - 1) % chunk + 1) * AG * (ak + av) * 2, ms, kernel=kernel, batch=batch, context=context)
-    q = torch.randn((rows, AH * ak), device=device).to(bf)
-    qw = torch.ones(AH * ak, device=device).to(bf)
-    ms = timed(lambda: blocks.kv_prepare(q.unflatten(1, (1, AH * ak)), None, None, q_norm=qw, eps=1e-6))
-    out["whole_projection_norm"] = stream(rows * AH * ak * 2 * 2, ms, rows=rows)
+    q, kk, vv = (torch.randn((rows, w), device=device).to(bf) for w in (AH * ak, AG * ak, AG * av))
+    qw, kw = torch.ones(AH * ak, device=device).to(bf), torch.ones(AG * ak, device=device).to(bf)
+    slab = torch.empty((rows // page, page, AG * (ak + av)), dtype=bf, device=device)
+    table = torch.arange(rows // page, dtype=torch.int32, device=device).view(1, -1)
+    pos, seq = torch.arange(rows, dtype=torch.int32, device=device), torch.zeros(rows, dtype=torch.int32, device=device)
+    ms = timed(lambda: blocks.qk_whole_prepare(q, kk, vv, heads=AH, kv_heads=AG, q_norm=qw, k_norm=kw, eps=1e-6, rot_dims=cfg["rot_dims"], base=5e4,
+                                               tok_pos=pos, tok_seq=seq, block_table=table, slab=slab))
+    out["whole_norm_rotation_cache_store"] = stream(rows * (AH * ak * 2 + AG * (ak + av) * 2) * 2, ms, rows=rows)
     ff = cfg["ff"]
     gu = torch.randn((rows // 4, 2 * ff), device=device).to(bf)
     ms = timed(lambda: blocks.gated_act(gu, blocks.ACT_CLAMPED_SWISH, cfg["limit"], 1.702))

@@ -137,6 +137,15 @@ int tlb_kv_prepare(void *q, long long q_token, long long q_head, int heads, cons
                    const int32_t *tok_pos, const int32_t *tok_seq, const int32_t *block_table, int max_pages, int num_pages, int page_size,
                    void *slab, int tokens, int dtype, void *stream);
 
+/* The same step for attention whose queries and keys are RMS-normed over the WHOLE projection (all heads of a token as one
+ * row; q_norm [heads * dk], k_norm [kv_heads * dk], NULL = no norm) and then rotated on the first rot_dims entries of every
+ * head (pairs (2i, 2i+1) if interleaved, else (i, i + rot_dims/2); rot_dims 0 = no rotation): q [T, heads * dk] rows q_token
+ * apart, changed in place; k [T, kv_heads * dk] and v [T, kv_heads * dv] (NULL: queries only) go to the token's slot. */
+int tlb_qk_whole_prepare(void *q, long long q_token, int heads, const void *q_norm, const void *k, long long k_token, const void *v, long long v_token,
+                          int kv_heads, int dk, int dv, const void *k_norm, float eps, int rot_dims, int interleaved, double base, const int32_t *tok_pos,
+                          const int32_t *tok_seq, const int32_t *block_table, int max_pages, int num_pages, int page_size, void *slab, int tokens, int dtype,
+                          void *stream);
+
 /* Linear attention with a decay, state in fp32 slots.  Per sequence and head S [dk, dv]:
  *   alpha = sigmoid(z + z_bias)^(1 / tau) per key channel, or (head_decay != NULL; z may be NULL) the fixed head_decay[head];
  *   S <- diag(alpha) S + k v^T;  out = S^T (q_scale * q)

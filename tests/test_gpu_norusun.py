@@ -265,6 +265,42 @@ def test_clamped_gate_and_tanh_rows(dev, dtype):
     close(blocks.act_rows(gu.to(dev), blocks.ACT_TANH), torch.tanh(gu.double()), tol)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("interleaved", [False, True])
+@pytest.mark.parametrize("heads,kv_heads,dk,dv,dims", [(4, 2, 16, 24, 16), (6, 3, 12, 10, 6), (1, 1, 64, 8, 2), (5, 5, 8, 8, 0), (16, 2, 128, 64, 128)])
+def test_norm_over_the_whole_projection_then_rotation_then_the_cache(dev, dtype, interleaved, heads, kv_heads, dk, dv, dims):
+    g = torch.Generator().manual_seed(heads * 31 + dk)
+    T, eps, base, page = 70, 1e-5, 5e4, 32
+    wide = torch.randn(T, heads * dk + kv_heads * (dk + dv) + 5, generator=g).to(dtype)   # q | k | v as columns of one product
+    q, k, v = wide[:, : heads * dk], wide[:, heads * dk : (heads + kv_heads) * dk], wide[:, (heads + kv_heads) * dk : (heads + kv_heads) * dk + kv_heads * dv]
+    wq, wk = (1 + 0.3 * torch.randn(heads * dk, generator=g)).to(dtype), (1 + 0.3 * torch.randn(kv_heads * dk, generator=g)).to(dtype)
+    start = 1000                                                                              # positions far from 0, across a page border
+    layout = "interleaved" if interleaved else "half"
+
+    def turned(x, w, n):
+        y = (O.rms_unit(x.double(), eps) * w.double()).view(T, n, dk)
+        full = torch.zeros(start + T, n, dk, dtype=D64)
+        full[start:] = y
+        return (O.rotate(full, dims=dims, base=base, layout=layout)[start:] if dims else y).reshape(T, n * dk)
+
+    want_q, want_k = turned(q, wq, heads), turned(k, wk, kv_heads)
+    wd = wide.to(dev)
+    qd, kd, vd = wd[:, : heads * dk], wd[:, heads * dk : (heads + kv_heads) * dk], wd[:, (heads + kv_heads) * dk : (heads + kv_heads) * dk + kv_heads * dv]
+    pages = (start + T) // page + 1
+    slab = torch.zeros((pages, page, kv_heads * (dk + dv)), dtype=dtype, device=dev)
+    table = torch.arange(pages - 1, -1, -1, dtype=torch.int32, device=dev).reshape(1, -1)    # pages in reverse order
+    pos = torch.arange(start, start + T, dtype=torch.int32, device=dev)
+    seq = torch.zeros(T, dtype=torch.int32, device=dev)
+    blocks.qk_whole_prepare(qd, kd, vd, heads=heads, kv_heads=kv_heads, q_norm=wq.to(dev), k_norm=wk.to(dev), eps=eps, rot_dims=dims, base=base,
+                            interleaved=interleaved, tok_pos=pos, tok_seq=seq, block_table=table, slab=slab)
+    tol = 3e-6 if dtype == torch.float32 else 1e-2
+    close(qd, want_q, tol)
+    rows = torch.stack([slab[pages - 1 - p // page, p % page] for p in range(start, start + T)])
+    close(rows[:, : kv_heads * dk], want_k, tol)
+    assert torch.equal(rows[:, kv_heads * dk :].cpu(), v)
+    assert torch.equal(kd.cpu(), k) and float(wd[:, -5:].float().sub(wide[:, -5:].float().to(dev)).abs().max()) == 0.0   # keys and neighbours untouched
+
+
 def fill_cache(dev, rows, page_size, dtype):
     """rows [T, width] -> (slab, block_table) with the tokens' pages in a scrambled order."""
     T, width = rows.shape

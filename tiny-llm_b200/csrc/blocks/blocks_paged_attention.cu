@@ -212,6 +212,64 @@ kv_prepare_kernel(T *q, long long q_token, long long q_head, int heads, const T 
     }
 }
 
+// One CTA per token, for attention whose queries and keys are RMS-normed over the WHOLE projection (all heads as one row,
+// weights of that size) and then rotated: the row is read once into shared memory as fp32, its sum of squares reduced by the
+// CTA, and norm, weight and rotation (the first rot_dims entries of every head by the token's position; pairs (2i, 2i+1) or
+// (i, i + rot_dims/2); angles evaluated in double once per token) are applied on the way out - the queries back in place,
+// keys and values to the token's slot of the cache.  Nothing is rounded between the norm and the rotation.
+template <typename T>
+__global__ void __launch_bounds__(256)
+qk_whole_prepare_kernel(T *q, long long q_token, int heads, const T *__restrict__ q_norm, const T *__restrict__ k, long long k_token,
+                        const T *__restrict__ v, long long v_token, int kv_heads, int dk, int dv, const T *__restrict__ k_norm, float eps, int rot_dims,
+                        int interleaved, double log2_base, const int32_t *__restrict__ tok_pos, const int32_t *__restrict__ tok_seq,
+                        const int32_t *__restrict__ block_table, int max_pages, int num_pages, int page_size, T *__restrict__ slab) {
+    extern __shared__ float srow[];  // [max(heads, kv_heads) * dk] the row, then [rot_dims] cos | sin
+    __shared__ float scratch[33];
+    const int t = blockIdx.x, pos = tok_pos[t], half = rot_dims / 2;
+    const int longest = max(heads, kv_heads) * dk;
+    float *cs = srow + longest, *sn = cs + half;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) rope_angle(pos, i, rot_dims, log2_base, cs[i], sn[i]);
+    T *dst = nullptr;
+    if (k != nullptr) {
+        const int page = block_table[(size_t)tok_seq[t] * max_pages + pos / page_size];
+        if (page >= 0 && page < num_pages) dst = slab + ((size_t)page * page_size + pos % page_size) * ((size_t)kv_heads * (dk + dv));
+    }
+    for (int which = 0; which < 2; ++which) {  // 0: queries (in place), 1: keys (to the cache)
+        const int nh = which == 0 ? heads : kv_heads;
+        const T *src = which == 0 ? q + (size_t)t * q_token : (k ? k + (size_t)t * k_token : nullptr);
+        const T *w = which == 0 ? q_norm : k_norm;
+        T *out = which == 0 ? q + (size_t)t * q_token : dst;
+        if (src == nullptr) continue;  // uniform over the CTA
+        const int width = nh * dk;
+        float ss = 0.f;
+        __syncthreads();
+        for (int d = threadIdx.x; d < width; d += blockDim.x) {
+            float x = to_f(src[d]);
+            srow[d] = x;
+            ss = fmaf(x, x, ss);
+        }
+        ss = block_sum(ss, scratch);  // (its barriers also publish srow and the angles)
+        const float inv = w ? 1.0f / sqrtf(ss / (float)width + eps) : 1.f;
+        if (out == nullptr) continue;
+        for (int d = threadIdx.x; d < width; d += blockDim.x) {
+            const int e = d % dk;
+            float x = srow[d] * inv * (w ? to_f(w[d]) : 1.f);
+            if (e < rot_dims) {
+                const bool low = interleaved ? !(e & 1) : e < half;
+                const int i = interleaved ? e >> 1 : (low ? e : e - half);
+                const int od = interleaved ? (d ^ 1) : (low ? d + half : d - half);
+                const float other = srow[od] * inv * (w ? to_f(w[od]) : 1.f);
+                x = low ? x * cs[i] - other * sn[i] : x * cs[i] + other * sn[i];
+            }
+            out[d] = from_f<T>(x);
+        }
+    }
+    if (dst != nullptr) {
+        const T *vr = v + (size_t)t * v_token;
+        for (int d = threadIdx.x; d < kv_heads * dv; d += blockDim.x) dst[(size_t)kv_heads * dk + d] = vr[d];
+    }
+}
+
 template <typename T, int VL>
 static int pa_launch(const void *q, long long q_token, long long q_head, const void *slab, int num_pages, int page_size, int dk, int dv, int heads,
                      int kv_heads, const int32_t *block_table, int max_pages, const int32_t *tiles, int num_tiles, const int32_t *tok_pos, int mask,
@@ -284,6 +342,36 @@ int tlb_kv_prepare(void *q, long long q_token, long long q_head, int heads, cons
                                                                             (const T *)v, v_token, v_head, kv_heads, dk, dv, (const T *)k_norm, eps,
                                                                             tok_pos, tok_seq, block_table, max_pages, num_pages, page_size, (T *)slab));
     TL_LAUNCH_CHECK("kv_prepare");
+    return TL_OK;
+}
+
+int tlb_qk_whole_prepare(void *q, long long q_token, int heads, const void *q_norm, const void *k, long long k_token, const void *v, long long v_token,
+                          int kv_heads, int dk, int dv, const void *k_norm, float eps, int rot_dims, int interleaved, double base, const int32_t *tok_pos,
+                          const int32_t *tok_seq, const int32_t *block_table, int max_pages, int num_pages, int page_size, void *slab, int tokens, int dtype,
+                          void *stream) {
+    if (tokens <= 0) return TL_OK;
+    if (!q || !tok_pos || heads <= 0 || dk <= 0 || rot_dims < 0 || (rot_dims & 1) || rot_dims > dk || (rot_dims > 0 && !(base > 0)))
+        return tl::fail(TL_EINVAL, "qk_whole_prepare: bad argument");
+    if (k && (!v || !slab || !tok_seq || !block_table || kv_heads <= 0 || dv <= 0 || page_size <= 0 || max_pages <= 0))
+        return tl::fail(TL_EINVAL, "qk_whole_prepare: bad cache argument");
+    if (!k) kv_heads = 0;
+    size_t smem = ((size_t)(heads > kv_heads ? heads : kv_heads) * dk + rot_dims) * sizeof(float);
+    if (smem > 200 * 1024) return tl::fail(TL_EINVAL, "qk_whole_prepare: a projection of %d entries does not fit in shared memory", heads * dk);
+    double lb = rot_dims > 0 ? log2(base) : 0.0;
+#define TLB_QK                                                                                                                                      \
+    do {                                                                                                                                            \
+        auto kernel = qk_whole_prepare_kernel<T>;                                                                                                   \
+        if (smem > 48 * 1024) {                                                                                                                     \
+            cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                                   \
+            if (e != cudaSuccess) return tl::fail(TL_ECUDA, "qk_whole_prepare: %s", cudaGetErrorString(e));                                         \
+        }                                                                                                                                           \
+        kernel<<<tokens, 256, smem, as_stream(stream)>>>((T *)q, q_token, heads, (const T *)q_norm, (const T *)k, k_token, (const T *)v, v_token, kv_heads, \
+                                                         dk, dv, (const T *)k_norm, eps, rot_dims, interleaved, lb, tok_pos, tok_seq, block_table,    \
+                                                         max_pages, num_pages, page_size, (T *)slab);                                               \
+    } while (0)
+    TLB_DISPATCH(dtype, "qk_whole_prepare", TLB_QK);
+#undef TLB_QK
+    TL_LAUNCH_CHECK("qk_whole_prepare");
     return TL_OK;
 }
 

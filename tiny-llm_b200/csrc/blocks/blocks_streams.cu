@@ -19,11 +19,37 @@ namespace tlb {
 
 constexpr int kMaxStreams = 8;
 
-template <typename T>
+template <typename T> struct Pack4;
+template <> struct Pack4<float> {
+    static __device__ __forceinline__ void store(float *p, float4 v) { *reinterpret_cast<float4 *>(p) = v; }
+    static __device__ __forceinline__ float4 load(const float *p) { return *reinterpret_cast<const float4 *>(p); }
+};
+template <> struct Pack4<bf16> {
+    static __device__ __forceinline__ void store(bf16 *p, float4 v) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 u;
+        u.x = *reinterpret_cast<uint32_t *>(&a), u.y = *reinterpret_cast<uint32_t *>(&b);
+        *reinterpret_cast<uint2 *>(p) = u;
+    }
+    static __device__ __forceinline__ float4 load(const bf16 *p) {
+        uint2 u = *reinterpret_cast<const uint2 *>(p);
+        float2 a = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&u.x)), b = __bfloat1622float2(*reinterpret_cast<__nv_bfloat162 *>(&u.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+};
+
+// V = 4: four adjacent columns per thread and step (16-byte accesses; dim % 4 == 0), the sublayer's input kept in registers
+// between the two sweeps when the row fits (dim <= 4 * kKeep * 256); V = 1: any dim, the second sweep reads the row again.
+// The arithmetic per column is the same in both, so a row's result does not depend on which one ran.
+constexpr int kKeep = 4;
+
+template <typename T, int N /* streams, 0 = any number up to kMaxStreams */, int V>
 __global__ void __launch_bounds__(256)
 streams_step_kernel(float *xs, const float *__restrict__ x0, const float *__restrict__ y, const T *__restrict__ y_bias,
                     const float *__restrict__ write_w /* mix [n, n] (from, to), then out [n] */,
-                    const float *__restrict__ read_w /* in [n], then the norm's weight */, float eps, T *__restrict__ h, int n, int dim) {
+                    const float *__restrict__ read_w /* in [n], then the norm's weight */, float eps, T *__restrict__ h, int n_any, int dim) {
+    constexpr int NM = N ? N : kMaxStreams;
+    const int n = N ? N : n_any;
     __shared__ float scratch[33];
     __shared__ float sw[kMaxStreams * kMaxStreams + 2 * kMaxStreams + 1];
     float *mix = sw, *outw = sw + kMaxStreams * kMaxStreams, *inw = outw + kMaxStreams;
@@ -35,49 +61,99 @@ streams_step_kernel(float *xs, const float *__restrict__ x0, const float *__rest
     const size_t row = blockIdx.x;
     float *xr = xs + row * n * dim;
     float ss = 0.f;
-    for (int d = threadIdx.x; d < dim; d += blockDim.x) {
-        float x[kMaxStreams], nx[kMaxStreams];
+    float keep[V == 4 ? kKeep : 1][V];
+    const bool kept = V == 4 && dim <= 4 * kKeep * 256;
+    int step = 0;
+    for (int d = threadIdx.x * V; d < dim; d += blockDim.x * V, ++step) {
+        float x[NM][V], nx[NM][V], yv[V];
 #pragma unroll
-        for (int s = 0; s < kMaxStreams; ++s)
-            if (s < n) x[s] = x0 ? x0[row * dim + d] : xr[(size_t)s * dim + d];
+        for (int s = 0; s < NM; ++s) {
+            if (s < n) {
+                const float *src = x0 ? x0 + row * dim + d : xr + (size_t)s * dim + d;
+                if (V == 4) {
+                    float4 t = *reinterpret_cast<const float4 *>(src);
+                    x[s][0] = t.x, x[s][1 % V] = t.y, x[s][2 % V] = t.z, x[s][3 % V] = t.w;
+                } else x[s][0] = src[0];
+            }
+        }
         if (write_w) {
-            const float yv = y[row * dim + d] + (y_bias ? to_f(y_bias[d]) : 0.f);
+            if (V == 4) {
+                float4 t = *reinterpret_cast<const float4 *>(y + row * dim + d);
+                yv[0] = t.x, yv[1 % V] = t.y, yv[2 % V] = t.z, yv[3 % V] = t.w;
+                if (y_bias) {
+                    float4 b = Pack4<T>::load(y_bias + d);
+                    yv[0] += b.x, yv[1 % V] += b.y, yv[2 % V] += b.z, yv[3 % V] += b.w;
+                }
+            } else yv[0] = y[row * dim + d] + (y_bias ? to_f(y_bias[d]) : 0.f);
 #pragma unroll
-            for (int t = 0; t < kMaxStreams; ++t) {
+            for (int t = 0; t < NM; ++t) {
                 if (t < n) {
-                    float acc = 0.f;
 #pragma unroll
-                    for (int s = 0; s < kMaxStreams; ++s)
-                        if (s < n) acc = fmaf(mix[s * n + t], x[s], acc);
-                    nx[t] = fmaf(outw[t], yv, acc);
+                    for (int v = 0; v < V; ++v) {
+                        float acc = 0.f;
+#pragma unroll
+                        for (int s = 0; s < NM; ++s)
+                            if (s < n) acc = fmaf(mix[s * n + t], x[s][v], acc);
+                        nx[t][v] = fmaf(outw[t], yv[v], acc);
+                    }
                 }
             }
         } else {
 #pragma unroll
-            for (int s = 0; s < kMaxStreams; ++s) nx[s] = x[s];
+            for (int s = 0; s < NM; ++s)
+#pragma unroll
+                for (int v = 0; v < V; ++v) nx[s][v] = x[s][v];
         }
         if (write_w || x0) {
 #pragma unroll
-            for (int s = 0; s < kMaxStreams; ++s)
-                if (s < n) xr[(size_t)s * dim + d] = nx[s];
+            for (int s = 0; s < NM; ++s) {
+                if (s < n) {
+                    if (V == 4) *reinterpret_cast<float4 *>(xr + (size_t)s * dim + d) = make_float4(nx[s][0], nx[s][1 % V], nx[s][2 % V], nx[s][3 % V]);
+                    else xr[(size_t)s * dim + d] = nx[s][0];
+                }
+            }
         }
         if (read_w) {
-            float u = 0.f;
 #pragma unroll
-            for (int s = 0; s < kMaxStreams; ++s)
-                if (s < n) u = fmaf(inw[s], nx[s], u);
-            ss = fmaf(u, u, ss);
+            for (int v = 0; v < V; ++v) {
+                float u = 0.f;
+#pragma unroll
+                for (int s = 0; s < NM; ++s)
+                    if (s < n) u = fmaf(inw[s], nx[s][v], u);
+                ss = fmaf(u, u, ss);
+                if (V == 4 && kept) {
+#pragma unroll
+                    for (int kk = 0; kk < kKeep; ++kk)
+                        if (kk == step) keep[kk % (V == 4 ? kKeep : 1)][v] = u;
+                }
+            }
         }
     }
     if (!read_w) return;
     ss = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(ss / (float)dim + eps) * inw[n];
-    for (int d = threadIdx.x; d < dim; d += blockDim.x) {  // the thread's own columns again (it wrote them itself)
-        float u = 0.f;
+    step = 0;
+    for (int d = threadIdx.x * V; d < dim; d += blockDim.x * V, ++step) {  // the thread's own columns again (it wrote them itself)
+        float u[V];
+        if (V == 4 && kept) {
 #pragma unroll
-        for (int s = 0; s < kMaxStreams; ++s)
-            if (s < n) u = fmaf(inw[s], xr[(size_t)s * dim + d], u);
-        h[row * dim + d] = from_f<T>(u * inv);
+            for (int kk = 0; kk < kKeep; ++kk)
+                if (kk == step) {
+#pragma unroll
+                    for (int v = 0; v < V; ++v) u[v] = keep[kk % (V == 4 ? kKeep : 1)][v];
+                }
+        } else {
+#pragma unroll
+            for (int v = 0; v < V; ++v) {
+                float a = 0.f;
+#pragma unroll
+                for (int s = 0; s < NM; ++s)
+                    if (s < n) a = fmaf(inw[s], xr[(size_t)s * dim + d + v], a);
+                u[v] = a;
+            }
+        }
+        if (V == 4) Pack4<T>::store(h + row * dim + d, make_float4(u[0] * inv, u[1 % V] * inv, u[2 % V] * inv, u[3 % V] * inv));
+        else h[row * dim + d] = from_f<T>(u[0] * inv);
     }
 }
 
@@ -124,8 +200,14 @@ int tlb_streams_step(float *xs, const float *x0, const float *y, const void *y_b
     if (!xs || streams <= 0 || dim <= 0 || (write_w && !y) || (read_w && !h) || (!write_w && !read_w && !x0))
         return tl::fail(TL_EINVAL, "streams_step: bad argument");
     if (streams > kMaxStreams) return tl::fail(TL_EINVAL, "streams_step: %d streams > %d", streams, kMaxStreams);
-    TLB_DISPATCH(dtype, "streams_step",
-                 streams_step_kernel<T><<<rows, 256, 0, as_stream(stream)>>>(xs, x0, y, (const T *)y_bias, write_w, read_w, eps, (T *)h, streams, dim));
+    // 16-byte accesses when every row of every operand starts on such a boundary
+    const bool wide = dim % 4 == 0 && (uintptr_t)xs % 16 == 0 && (uintptr_t)x0 % 16 == 0 && (uintptr_t)y % 16 == 0 && (uintptr_t)y_bias % 8 == 0 &&
+                      (uintptr_t)h % 8 == 0;
+#define TLB_SS(NV, VV) streams_step_kernel<T, NV, VV><<<rows, 256, 0, as_stream(stream)>>>(xs, x0, y, (const T *)y_bias, write_w, read_w, eps, (T *)h, streams, dim)
+#define TLB_SS_N(VV) do { if (streams == 1) TLB_SS(1, VV); else if (streams == 2) TLB_SS(2, VV); else if (streams == 4) TLB_SS(4, VV); else TLB_SS(0, VV); } while (0)
+    TLB_DISPATCH(dtype, "streams_step", if (wide) TLB_SS_N(4); else TLB_SS_N(1));
+#undef TLB_SS_N
+#undef TLB_SS
     TL_LAUNCH_CHECK("streams_step");
     return TL_OK;
 }

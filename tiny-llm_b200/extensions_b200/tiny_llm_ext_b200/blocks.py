@@ -53,6 +53,7 @@ _SIGNATURES = {
                                      ctypes.c_size_t, _VP, _I, _VP]),
     "tlb_paged_attention_mma_workspace": (ctypes.c_size_t, [_I, _I, _I, _I, _I]),
     "tlb_kv_prepare": (_I, [_VP, _LL, _LL, _I, _VP, _VP, _LL, _LL, _VP, _LL, _LL, _I, _I, _I, _VP, _F, _VP, _VP, _VP, _I, _I, _I, _VP, _I, _I, _VP]),
+    "tlb_qk_whole_prepare": (_I, [_VP, _LL, _I, _VP, _VP, _LL, _VP, _LL, _I, _I, _I, _VP, _F, _I, _I, _D, _VP, _VP, _VP, _I, _I, _I, _VP, _I, _I, _VP]),
     "tlb_decay_scan_workspace": (ctypes.c_size_t, [_I, _I, _I, _I, _I]),
     "tlb_decay_scan": (_I, [_VP, _LL, _LL, _VP, _LL, _LL, _VP, _LL, _LL, _VP, _LL, _VP, _F, _VP, _VP, _VP, _I, _I, _F, _I, _I, _I, _VP, _I, _I, _VP, _LL, _I,
                             _VP, _VP, ctypes.c_size_t, _I, _VP, _VP, _I, _VP, _I, _VP]),
@@ -475,6 +476,31 @@ def kv_prepare(q, k, v, *, q_norm=None, k_norm=None, eps: float = 0.0, tok_pos=N
                                     k.stride(1) if k is not None else 0, _ptr(v), v.stride(0) if v is not None else 0, v.stride(1) if v is not None else 0,
                                     G, dk, max(dv, 1), _ptr(k_norm), float(eps), _ptr(tok_pos), _ptr(tok_seq), _ptr(block_table),
                                     block_table.shape[1] if block_table is not None else 0, P, page_size, _ptr(slab), T, _code(q.dtype), _stream(q)))
+
+
+def qk_whole_prepare(q, k, v, *, heads: int, kv_heads: int, q_norm=None, k_norm=None, eps: float = 0.0, rot_dims: int = 0, base: float = 10000.0,
+                     interleaved: bool = False, tok_pos, tok_seq=None, block_table=None, slab=None):
+    """``q [T, heads * dk]`` (a view, changed in place), ``k [T, kv_heads * dk]``, ``v [T, kv_heads * dv]`` (views, or None for
+    queries only): RMS norms over the WHOLE projection (weights of that size), rotation of the first ``rot_dims`` entries of
+    every head by the token's position, keys and values stored at the token's slot of ``slab [P, page, kv_heads * (dk + dv)]``."""
+    _gpu("qk_whole_prepare", q, k, v, q_norm, k_norm, tok_pos, tok_seq, block_table, slab)
+    T = q.shape[0]
+    dk = q.shape[1] // heads
+    dv = 0
+    if q.stride(1) != 1 or q.shape[1] != heads * dk or (q_norm is not None and (q_norm.shape != (heads * dk,) or q_norm.dtype != q.dtype)):
+        raise RuntimeError("qk_whole_prepare: queries [T, heads * dk] with unit inner stride, a norm weight of that width")
+    P = page_size = 0
+    if k is not None:
+        dv = v.shape[1] // kv_heads
+        P, page_size, width = slab.shape
+        if k.shape != (T, kv_heads * dk) or v.shape != (T, kv_heads * dv) or width != kv_heads * (dk + dv) or not (q.dtype == k.dtype == v.dtype == slab.dtype):
+            raise RuntimeError("qk_whole_prepare: keys, values and cache do not match")
+        if k.stride(1) != 1 or v.stride(1) != 1 or not slab.is_contiguous() or (k_norm is not None and (k_norm.shape != (kv_heads * dk,) or k_norm.dtype != q.dtype)):
+            raise RuntimeError("qk_whole_prepare: unit inner strides, a norm weight of the keys' width")
+    _check(library().tlb_qk_whole_prepare(_ptr(q), q.stride(0), heads, _ptr(q_norm), _ptr(k), k.stride(0) if k is not None else 0, _ptr(v),
+                                          v.stride(0) if v is not None else 0, kv_heads if k is not None else 0, dk, max(dv, 1), _ptr(k_norm), float(eps),
+                                          int(rot_dims), int(bool(interleaved)), float(base), _ptr(tok_pos), _ptr(tok_seq), _ptr(block_table),
+                                          block_table.shape[1] if block_table is not None else 0, P, page_size, _ptr(slab), T, _code(q.dtype), _stream(q)))
 
 
 def paged_attention(q, slab, block_table, tiles, tok_pos, *, kv_heads: int, dv: int, mask: int, mask_size: int, scale: float, softcap: float = 0.0,

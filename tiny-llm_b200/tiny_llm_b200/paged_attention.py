@@ -99,21 +99,28 @@ class PagedGroupedAttention:
         T, H, G = q.shape[0], self.heads, self.kv_heads
         q3 = q.unflatten(1, (H, self.dim))
         q_norm, k_norm = self.q_norm, self.k_norm
-        if self.whole_norm:  # each projection as ONE row: normed in place before anything else touches it
-            blocks.kv_prepare(q.unflatten(1, (1, H * self.dim)), None, None, q_norm=q_norm, eps=self.eps)
-            if self.caches and k_norm is not None:
-                blocks.kv_prepare(k.unflatten(1, (1, G * self.dim)), None, None, q_norm=k_norm, eps=self.eps)
-            q_norm = k_norm = None
-        if self.rot is not None:
-            r = self.rot
-            blocks.rope_rows(q, plan.tok_pos, heads=H, head_stride=self.dim, first=0, dims=r["dims"], base=r["base"], interleaved=r["interleaved"], factor=r["factor"])
+        if self.whole_norm and (self.rot is None or self.rot["factor"] == 1.0):
+            # each projection as ONE row: norm, rotation and the store into the cache in one launch
+            r = self.rot or {"dims": 0, "base": 1.0, "interleaved": False}
+            blocks.qk_whole_prepare(q, k if self.caches else None, v if self.caches else None, heads=H, kv_heads=G, q_norm=q_norm,
+                                    k_norm=k_norm if self.caches else None, eps=self.eps, rot_dims=r["dims"], base=r["base"], interleaved=r["interleaved"],
+                                    tok_pos=plan.tok_pos, tok_seq=plan.tok_seq, block_table=plan.block_table, slab=slab if self.caches else None)
+        else:
+            if self.whole_norm:  # scaled positions: the row norms alone, then the framework's rotation and store
+                blocks.kv_prepare(q.unflatten(1, (1, H * self.dim)), None, None, q_norm=q_norm, eps=self.eps)
+                if self.caches and k_norm is not None:
+                    blocks.kv_prepare(k.unflatten(1, (1, G * self.dim)), None, None, q_norm=k_norm, eps=self.eps)
+                q_norm = k_norm = None
+            if self.rot is not None:
+                r = self.rot
+                blocks.rope_rows(q, plan.tok_pos, heads=H, head_stride=self.dim, first=0, dims=r["dims"], base=r["base"], interleaved=r["interleaved"], factor=r["factor"])
+                if self.caches:
+                    blocks.rope_rows(k, plan.tok_pos, heads=G, head_stride=self.dim, first=0, dims=r["dims"], base=r["base"], interleaved=r["interleaved"], factor=r["factor"])
             if self.caches:
-                blocks.rope_rows(k, plan.tok_pos, heads=G, head_stride=self.dim, first=0, dims=r["dims"], base=r["base"], interleaved=r["interleaved"], factor=r["factor"])
-        if self.caches:
-            blocks.kv_prepare(q3, k.unflatten(1, (G, self.dim)), v.unflatten(1, (G, self.vdim)), q_norm=q_norm, k_norm=k_norm, eps=self.eps,
-                              tok_pos=plan.tok_pos, tok_seq=plan.tok_seq, block_table=plan.block_table, slab=slab)
-        elif q_norm is not None:
-            blocks.kv_prepare(q3, None, None, q_norm=q_norm, eps=self.eps)
+                blocks.kv_prepare(q3, k.unflatten(1, (G, self.dim)), v.unflatten(1, (G, self.vdim)), q_norm=q_norm, k_norm=k_norm, eps=self.eps,
+                                  tok_pos=plan.tok_pos, tok_seq=plan.tok_seq, block_table=plan.block_table, slab=slab)
+            elif q_norm is not None:
+                blocks.kv_prepare(q3, None, None, q_norm=q_norm, eps=self.eps)
         o = blocks.paged_attention(q3, slab, plan.block_table, plan.tiles_for(self.tile_tokens), plan.tok_pos, kv_heads=G, dv=self.vdim, mask=self.mask,
                                    mask_size=self.mask_size, scale=self.scale, softcap=self.softcap, sink=self.sink, gate=gate, kernel=self.kernel,
                                    max_context=getattr(plan, "max_context", 0), head_bias=self.head_bias, weights=self.weights)
