@@ -1463,12 +1463,13 @@ def _norusun_kernels(cfg: dict, device, prompt: int, batch: int, context: int) -
     h = torch.randn((rows, D), device=device).to(bf)
     taps = torch.randn((D, K), device=device).to(bf)
     hist = torch.zeros((batch, D, K - 1), device=device)
-    ms = timed(lambda: blocks.short_conv(h, taps, seq_info=seqs_info(rows, 1, 0), state=hist, max_tokens=rows, act=0, add_input=True))
+    one_long, many_short = seqs_info(rows, 1, 0), seqs_info(1, batch, context)
+    ms = timed(lambda: blocks.short_conv(h, taps, seq_info=one_long, state=hist, max_tokens=rows, act=0, add_input=True))
     out["input_conv_prefill"] = stream(rows * D * 2 * 2, ms, tokens=rows, channels=D)
-    ms = timed(lambda: blocks.short_conv(h[:batch], taps, seq_info=seqs_info(1, batch, context), state=hist, max_tokens=1, act=0, add_input=True))
+    ms = timed(lambda: blocks.short_conv(h[:batch], taps, seq_info=many_short, state=hist, max_tokens=1, act=0, add_input=True))
     out["input_conv_decode"] = stream(batch * D * (2 * 2 + (K - 1) * 4 * 2), ms, batch=batch)
     mu, shift = torch.rand((5, D), device=device).to(bf), torch.zeros((batch, D), device=device)
-    ms = timed(lambda: blocks.shift_mix(h, mu, seq_info=seqs_info(rows, 1, 0), state=shift, max_tokens=rows))
+    ms = timed(lambda: blocks.shift_mix(h, mu, seq_info=one_long, state=shift, max_tokens=rows))
     out["shift_mix_prefill"] = stream(rows * D * 2 * 6, ms, tokens=rows)
 
     WH, wd = cfg["wkv_heads"], cfg["wkv_dim"]
@@ -1507,7 +1508,7 @@ def _norusun_kernels(cfg: dict, device, prompt: int, batch: int, context: int) -
     xw = torch.randn((rows, channels + 64), device=device).to(bf)[:, 32 : 32 + channels]  # columns of a wider product, as in the model
     ctaps, cb = torch.randn((channels, SK), device=device).to(bf), torch.zeros(channels, device=device).to(bf)
     chist = torch.zeros((1, channels, SK - 1), device=device)
-    ms = timed(lambda: blocks.short_conv(xw, ctaps, seq_info=seqs_info(rows, 1, 0), state=chist, max_tokens=rows, act=1, bias=cb))
+    ms = timed(lambda: blocks.short_conv(xw, ctaps, seq_info=one_long, state=chist, max_tokens=rows, act=1, bias=cb))
     out["state_space_conv_prefill"] = stream(rows * channels * 2 * 2, ms, tokens=rows, channels=channels)
     o32, gate, nw = torch.randn((rows, SH * P), device=device), torch.randn((rows, SH * P), device=device).to(bf), torch.ones(SH * P, device=device).to(bf)
     parts = cfg["ss_norm_groups"]

@@ -190,11 +190,27 @@ decay_combine_kernel(const int32_t *__restrict__ seq_info, const float *__restri
     for (int e = blockIdx.z * blockDim.x + threadIdx.x; e < dk * dv; e += gridDim.z * blockDim.x) {
         const int row = e / dv;
         float S = (start > 0 && slot_ok) ? mine[e] : 0.f;
-        for (int c = 0; c + 1 < nseg; ++c) {
-            float *cell = seg_state + (((size_t)s * max_segments + c) * heads + head) * dk * dv + e;
-            float local = *cell;
-            *cell = S;
-            S = fmaf(seg_decay[(((size_t)s * max_segments + c) * heads + head) * dk + row], S, local);
+        // eight segments' local states and decays are fetched before the first of them is used: the walk is a chain of
+        // multiply-adds, not of memory round trips
+        constexpr int kAhead = 8;
+        for (int c0 = 0; c0 + 1 < nseg; c0 += kAhead) {
+            float local[kAhead], decay[kAhead];
+#pragma unroll
+            for (int u = 0; u < kAhead; ++u) {
+                const int c = c0 + u;
+                if (c + 1 < nseg) {
+                    local[u] = seg_state[(((size_t)s * max_segments + c) * heads + head) * dk * dv + e];
+                    decay[u] = seg_decay[(((size_t)s * max_segments + c) * heads + head) * dk + row];
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kAhead; ++u) {
+                const int c = c0 + u;
+                if (c + 1 < nseg) {
+                    seg_state[(((size_t)s * max_segments + c) * heads + head) * dk * dv + e] = S;
+                    S = fmaf(decay[u], S, local[u]);
+                }
+            }
         }
         seg_state[(((size_t)s * max_segments + (nseg - 1)) * heads + head) * dk * dv + e] = S;
     }
@@ -289,7 +305,7 @@ int tlb_decay_scan(const void *q, long long q_token, long long q_head, const voi
     }
     TLB_DS(1, max_segments);
     TL_LAUNCH_CHECK("decay_scan (local states)");
-    decay_combine_kernel<<<dim3(num_seqs, heads, ceil_div(dk * dv, 256 * 4)), 256, 0, st>>>(seq_info, state, slot_stride, num_slots, heads, dk, dv,
+    decay_combine_kernel<<<dim3(num_seqs, heads, ceil_div(dk * dv, 256)), 256, 0, st>>>(seq_info, state, slot_stride, num_slots, heads, dk, dv,
                                                                                            max_segments, seg_state, seg_decay);
     TL_LAUNCH_CHECK("decay_scan (combine)");
     TLB_DS(3, max_segments);
