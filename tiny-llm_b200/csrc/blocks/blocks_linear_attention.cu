@@ -63,6 +63,7 @@ decay_scan_kernel(const T *__restrict__ q, long long q_token, long long q_head, 
     __shared__ float4 sx[kLaTokens * 4 * KR];  // per token and key channel: (decay, k, scaled q, -), one 16-byte read per row
     __shared__ float sv[kLaTokens * kLaCols];
     __shared__ float sprod[4 * KR];
+    __shared__ float2 s_step[kLaTokens];  // decay_kind 3: the token's (decay, step size), worked out once per token
     const int colblocks = (dv + kLaCols - 1) / kLaCols;
     const int s = blockIdx.x, head = blockIdx.y / colblocks, col0 = (blockIdx.y % colblocks) * kLaCols, c = blockIdx.z;
     const int seq_first = seq_info[s * 4 + 0], seq_count = seq_info[s * 4 + 1], start = seq_info[s * 4 + 2], slot = seq_info[s * 4 + 3];
@@ -95,17 +96,22 @@ decay_scan_kernel(const T *__restrict__ q, long long q_token, long long q_head, 
     for (int t0 = 0; t0 < count; t0 += kLaTokens) {
         const int n = min(kLaTokens, count - t0);
         __syncthreads();
+        if (decay_kind == 3) {
+            if (threadIdx.x < n) {
+                const float zz = z[(size_t)(first + t0 + threadIdx.x) * z_token + head] + (z_bias ? to_f(z_bias[head]) : 0.f);
+                const float dt = zz > 20.f ? zz : log1pf(expf(zz));
+                s_step[threadIdx.x] = make_float2(expf(-rate * dt), dt);
+            }
+            __syncthreads();
+        }
         for (int e = threadIdx.x; e < n * dk; e += blockDim.x) {
             int j = e / dk, d = e - j * dk;
             size_t tok = (size_t)(first + t0 + j);
             float alpha, kmul = 1.f;
             if (head_decay) alpha = head_decay[head];
             else if (decay_kind == 2) alpha = expf(-expf(z[tok * z_token + (size_t)head * dk + d] + (z_bias ? to_f(z_bias[(size_t)head * dk + d]) : 0.f)));
-            else if (decay_kind == 3) {
-                const float zz = z[tok * z_token + head] + (z_bias ? to_f(z_bias[head]) : 0.f);
-                const float dt = zz > 20.f ? zz : log1pf(expf(zz));
-                alpha = expf(-rate * dt), kmul = dt;
-            } else alpha = expf(log_sigmoid(z[tok * z_token + (size_t)head * dk + d] + (z_bias ? to_f(z_bias[(size_t)head * dk + d]) : 0.f)) * inv_tau);
+            else if (decay_kind == 3) alpha = s_step[j].x, kmul = s_step[j].y;
+            else alpha = expf(log_sigmoid(z[tok * z_token + (size_t)head * dk + d] + (z_bias ? to_f(z_bias[(size_t)head * dk + d]) : 0.f)) * inv_tau);
             const T *kp = k + tok * k_token + (size_t)qk_head * k_head, *qp = q + tok * q_token + (size_t)qk_head * q_head;
             float kd = to_f(kp[d]), qd = to_f(qp[d]);
             if (d < rope_dims) {  // rotate the pair this entry belongs to, in fp32, by the token's tabulated angle

@@ -260,19 +260,39 @@ __global__ void cast_rows_kernel(const float *__restrict__ src, T *__restrict__ 
     for (int i = threadIdx.x; i < dim; i += blockDim.x) d[i] = from_f<T>(s[i]);
 }
 
+__device__ __forceinline__ float gated_pair(float g, float u, int act, float limit, float slope) {
+    if (act == 3) {  // clamped: the gate from above, the other half on both sides; g sigmoid(slope g) (u + 1)
+        g = fminf(g, limit), u = fminf(fmaxf(u, -limit), limit);
+        return g / (1.0f + expf(-slope * g)) * (u + 1.0f);
+    }
+    return act_apply(g, act) * u;
+}
+
 template <typename T>
 __global__ void gated_act_kernel(const T *__restrict__ gu, T *__restrict__ out, long long total, int width, int act, float limit, float slope) {
     long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     long long row = i / width;
     int j = (int)(i - row * width);
-    float g = to_f(gu[row * 2 * width + j]), u = to_f(gu[row * 2 * width + width + j]);
-    if (act == 3) {  // clamped: the gate from above, the other half on both sides; g sigmoid(slope g) (u + 1)
-        g = fminf(g, limit), u = fminf(fmaxf(u, -limit), limit);
-        out[i] = from_f<T>(g / (1.0f + expf(-slope * g)) * (u + 1.0f));
-        return;
+    out[i] = from_f<T>(gated_pair(to_f(gu[row * 2 * width + j]), to_f(gu[row * 2 * width + width + j]), act, limit, slope));
+}
+
+// Eight adjacent columns per thread, 16-byte accesses (bf16, width % 8 == 0).
+__global__ void gated_act_wide_kernel(const bf16 *__restrict__ gu, bf16 *__restrict__ out, long long total8, int width, int act, float limit, float slope) {
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total8) return;
+    const int per_row = width / 8;
+    long long row = i / per_row;
+    int j = (int)(i - row * per_row) * 8;
+    uint4 g4 = *reinterpret_cast<const uint4 *>(gu + row * 2 * width + j), u4 = *reinterpret_cast<const uint4 *>(gu + row * 2 * width + width + j), o4;
+    const __nv_bfloat162 *gp = reinterpret_cast<const __nv_bfloat162 *>(&g4), *up = reinterpret_cast<const __nv_bfloat162 *>(&u4);
+    __nv_bfloat162 *op = reinterpret_cast<__nv_bfloat162 *>(&o4);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        float2 g = __bfloat1622float2(gp[e]), u = __bfloat1622float2(up[e]);
+        op[e] = __floats2bfloat162_rn(gated_pair(g.x, u.x, act, limit, slope), gated_pair(g.y, u.y, act, limit, slope));
     }
-    out[i] = from_f<T>(act_apply(g, act) * u);
+    *reinterpret_cast<uint4 *>(out + row * width + j) = o4;
 }
 
 __global__ void argmax_rows_kernel(const float *__restrict__ logits, int32_t *__restrict__ out, int vocab) {
@@ -405,8 +425,12 @@ int tlb_gated_act(const void *gu, void *out, int rows, int width, int act, float
     if (rows <= 0 || width <= 0) return TL_OK;
     if (!gu || !out || (act != 0 && act != 1 && act != 3) || (act == 3 && !(limit > 0.f))) return tl::fail(TL_EINVAL, "gated_act: bad argument");
     long long total = (long long)rows * width;
-    TLB_DISPATCH(dtype, "gated_act",
-                 gated_act_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, as_stream(stream)>>>((const T *)gu, (T *)out, total, width, act, limit, slope));
+    if (dtype == TL_BF16 && width % 8 == 0 && (uintptr_t)gu % 16 == 0 && (uintptr_t)out % 16 == 0) {
+        long long total8 = total / 8;
+        gated_act_wide_kernel<<<(unsigned)((total8 + 255) / 256), 256, 0, as_stream(stream)>>>((const bf16 *)gu, (bf16 *)out, total8, width, act, limit, slope);
+    } else
+        TLB_DISPATCH(dtype, "gated_act",
+                     gated_act_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, as_stream(stream)>>>((const T *)gu, (T *)out, total, width, act, limit, slope));
     TL_LAUNCH_CHECK("gated_act");
     return TL_OK;
 }

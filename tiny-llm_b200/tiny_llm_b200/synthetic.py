@@ -464,8 +464,7 @@ def norusun_config(*, width=96, vocab=200, pattern="LdPdWnLd", streams=2, canon_
                    limit=3.0, eps=1e-6) -> dict:
     """A config.json for a stack spelled by ``pattern``, two letters a layer: the mixer (``W`` time-mix linear attention,
     ``L`` latent attention, ``P`` chunked sigmoid attention beside a state-space mixer) and the feed-forward (``d`` dense,
-    ``n`` none).  ``streams`` 0 = no residual streams, ``canon_taps`` 0 = no input convolution.  ``width`` must equal
-    ``wkv_heads * wkv_dim`` when the stack has a ``W`` layer."""
+    ``n`` none).  ``streams`` 0 = no residual streams, ``canon_taps`` 0 = no input convolution."""
     if len(pattern) % 2:
         raise ValueError("the pattern is pairs of letters: mixer, feed-forward")
     layers = []
