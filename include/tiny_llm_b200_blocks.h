@@ -143,8 +143,9 @@ int tlb_kv_prepare(void *q, long long q_token, long long q_head, int heads, cons
  * apart, changed in place; k [T, kv_heads * dk] and v [T, kv_heads * dv] (NULL: queries only) go to the token's slot. */
 int tlb_qk_whole_prepare(void *q, long long q_token, int heads, const void *q_norm, const void *k, long long k_token, const void *v, long long v_token,
                           int kv_heads, int dk, int dv, const void *k_norm, float eps, int rot_dims, int interleaved, double base, const int32_t *tok_pos,
-                          const int32_t *tok_seq, const int32_t *block_table, int max_pages, int num_pages, int page_size, void *slab, int tokens, int dtype,
-                          void *stream);
+                          const int32_t *tok_seq, const int32_t *block_table, int max_pages, int num_pages, int page_size, void *slab,
+                          const float *rope_cos, const float *rope_sin, int tokens, int dtype, void *stream);
+/* rope_cos, rope_sin [T, rot_dims / 2] fp32 (tlb_rope_table of this step's tokens), or NULL: the kernel evaluates the angles itself. */
 
 /* Linear attention with a decay, state in fp32 slots.  Per sequence and head S [dk, dv]:
  *   alpha = sigmoid(z + z_bias)^(1 / tau) per key channel, or (head_decay != NULL; z may be NULL) the fixed head_decay[head];

@@ -299,6 +299,13 @@ def test_norm_over_the_whole_projection_then_rotation_then_the_cache(dev, dtype,
     close(rows[:, : kv_heads * dk], want_k, tol)
     assert torch.equal(rows[:, kv_heads * dk :].cpu(), v)
     assert torch.equal(kd.cpu(), k) and float(wd[:, -5:].float().sub(wide[:, -5:].float().to(dev)).abs().max()) == 0.0   # keys and neighbours untouched
+    if dims:  # the angles read from the step's table instead of evaluated in the kernel: the same numbers
+        again, slab2 = wide.to(dev), torch.zeros_like(slab)
+        blocks.qk_whole_prepare(again[:, : heads * dk], again[:, heads * dk : (heads + kv_heads) * dk],
+                                again[:, (heads + kv_heads) * dk : (heads + kv_heads) * dk + kv_heads * dv], heads=heads, kv_heads=kv_heads, q_norm=wq.to(dev),
+                                k_norm=wk.to(dev), eps=eps, rot_dims=dims, base=base, interleaved=interleaved, tok_pos=pos, tok_seq=seq, block_table=table,
+                                slab=slab2, rope=blocks.rope_table(pos, dims=dims, base=base))
+        assert torch.equal(again, wd) and torch.equal(slab2, slab)
 
 
 def fill_cache(dev, rows, page_size, dtype):

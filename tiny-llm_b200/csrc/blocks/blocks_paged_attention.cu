@@ -222,13 +222,17 @@ __global__ void __launch_bounds__(256)
 qk_whole_prepare_kernel(T *q, long long q_token, int heads, const T *__restrict__ q_norm, const T *__restrict__ k, long long k_token,
                         const T *__restrict__ v, long long v_token, int kv_heads, int dk, int dv, const T *__restrict__ k_norm, float eps, int rot_dims,
                         int interleaved, double log2_base, const int32_t *__restrict__ tok_pos, const int32_t *__restrict__ tok_seq,
-                        const int32_t *__restrict__ block_table, int max_pages, int num_pages, int page_size, T *__restrict__ slab) {
+                        const int32_t *__restrict__ block_table, int max_pages, int num_pages, int page_size, T *__restrict__ slab,
+                        const float *__restrict__ rope_cos, const float *__restrict__ rope_sin /* [T, rot_dims / 2] tabulated, or NULL */) {
     extern __shared__ float srow[];  // [max(heads, kv_heads) * dk] the row, then [rot_dims] cos | sin
     __shared__ float scratch[33];
     const int t = blockIdx.x, pos = tok_pos[t], half = rot_dims / 2;
     const int longest = max(heads, kv_heads) * dk;
     float *cs = srow + longest, *sn = cs + half;
-    for (int i = threadIdx.x; i < half; i += blockDim.x) rope_angle(pos, i, rot_dims, log2_base, cs[i], sn[i]);
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        if (rope_cos) cs[i] = rope_cos[(size_t)t * half + i], sn[i] = rope_sin[(size_t)t * half + i];
+        else rope_angle(pos, i, rot_dims, log2_base, cs[i], sn[i]);
+    }
     T *dst = nullptr;
     if (k != nullptr) {
         const int page = block_table[(size_t)tok_seq[t] * max_pages + pos / page_size];
@@ -347,9 +351,10 @@ int tlb_kv_prepare(void *q, long long q_token, long long q_head, int heads, cons
 
 int tlb_qk_whole_prepare(void *q, long long q_token, int heads, const void *q_norm, const void *k, long long k_token, const void *v, long long v_token,
                           int kv_heads, int dk, int dv, const void *k_norm, float eps, int rot_dims, int interleaved, double base, const int32_t *tok_pos,
-                          const int32_t *tok_seq, const int32_t *block_table, int max_pages, int num_pages, int page_size, void *slab, int tokens, int dtype,
-                          void *stream) {
+                          const int32_t *tok_seq, const int32_t *block_table, int max_pages, int num_pages, int page_size, void *slab,
+                          const float *rope_cos, const float *rope_sin, int tokens, int dtype, void *stream) {
     if (tokens <= 0) return TL_OK;
+    if ((rope_cos == nullptr) != (rope_sin == nullptr)) return tl::fail(TL_EINVAL, "qk_whole_prepare: both rotation tables or neither");
     if (!q || !tok_pos || heads <= 0 || dk <= 0 || rot_dims < 0 || (rot_dims & 1) || rot_dims > dk || (rot_dims > 0 && !(base > 0)))
         return tl::fail(TL_EINVAL, "qk_whole_prepare: bad argument");
     if (k && (!v || !slab || !tok_seq || !block_table || kv_heads <= 0 || dv <= 0 || page_size <= 0 || max_pages <= 0))
@@ -367,7 +372,7 @@ int tlb_qk_whole_prepare(void *q, long long q_token, int heads, const void *q_no
         }                                                                                                                                           \
         kernel<<<tokens, 256, smem, as_stream(stream)>>>((T *)q, q_token, heads, (const T *)q_norm, (const T *)k, k_token, (const T *)v, v_token, kv_heads, \
                                                          dk, dv, (const T *)k_norm, eps, rot_dims, interleaved, lb, tok_pos, tok_seq, block_table,    \
-                                                         max_pages, num_pages, page_size, (T *)slab);                                               \
+                                                         max_pages, num_pages, page_size, (T *)slab, rope_cos, rope_sin);                           \
     } while (0)
     TLB_DISPATCH(dtype, "qk_whole_prepare", TLB_QK);
 #undef TLB_QK

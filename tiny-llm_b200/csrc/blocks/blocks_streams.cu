@@ -157,15 +157,15 @@ streams_step_kernel(float *xs, const float *__restrict__ x0, const float *__rest
     }
 }
 
-constexpr int kShiftChunk = 32;  // tokens per CTA
+constexpr int kShiftChunk = 32, kShiftSmallChunk = 8;  // tokens per CTA; the small one when the launch would leave SMs idle
 
 template <typename T>
 __global__ void __launch_bounds__(128)
 shift_mix_kernel(const T *__restrict__ h, long long h_token, const T *__restrict__ mu, int n, int dim, const int32_t *__restrict__ seq_info,
-                 float *__restrict__ state, long long slot_stride, int num_slots, T *__restrict__ out, long long out_part) {
+                 float *__restrict__ state, long long slot_stride, int num_slots, T *__restrict__ out, long long out_part, int chunk) {
     const int s = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
     const int first = seq_info[s * 4 + 0], count = seq_info[s * 4 + 1], start = seq_info[s * 4 + 2], slot = seq_info[s * 4 + 3];
-    const int lo = blockIdx.z * kShiftChunk, hi = min(count, lo + kShiftChunk);
+    const int lo = blockIdx.z * chunk, hi = min(count, lo + chunk);
     if (c >= dim || lo >= count) return;
     const bool slot_ok = slot >= 0 && slot < num_slots;
     float *mine = state + (size_t)(slot_ok ? slot : 0) * slot_stride + c;
@@ -217,10 +217,11 @@ int tlb_shift_mix(const void *h, long long h_token, const void *mu, int parts, i
     if (num_seqs <= 0) return TL_OK;
     if (!h || !mu || !seq_info || !state || !out || parts <= 0 || parts > 8 || dim <= 0 || max_tokens_per_seq <= 0 || num_slots <= 0)
         return tl::fail(TL_EINVAL, "shift_mix: bad argument");
-    dim3 grid(num_seqs, ceil_div(dim, 128), ceil_div(max_tokens_per_seq, kShiftChunk));
+    const int chunk = (long long)num_seqs * ceil_div(dim, 128) * ceil_div(max_tokens_per_seq, kShiftChunk) < 148 * 8 ? kShiftSmallChunk : kShiftChunk;
+    dim3 grid(num_seqs, ceil_div(dim, 128), ceil_div(max_tokens_per_seq, chunk));
     TLB_DISPATCH(dtype, "shift_mix",
                  shift_mix_kernel<T><<<grid, 128, 0, as_stream(stream)>>>((const T *)h, h_token, (const T *)mu, parts, dim, seq_info, state, slot_stride,
-                                                                           num_slots, (T *)out, out_part));
+                                                                           num_slots, (T *)out, out_part, chunk));
     TL_LAUNCH_CHECK("shift_mix");
     return TL_OK;
 }

@@ -53,7 +53,7 @@ _SIGNATURES = {
                                      ctypes.c_size_t, _VP, _I, _VP]),
     "tlb_paged_attention_mma_workspace": (ctypes.c_size_t, [_I, _I, _I, _I, _I]),
     "tlb_kv_prepare": (_I, [_VP, _LL, _LL, _I, _VP, _VP, _LL, _LL, _VP, _LL, _LL, _I, _I, _I, _VP, _F, _VP, _VP, _VP, _I, _I, _I, _VP, _I, _I, _VP]),
-    "tlb_qk_whole_prepare": (_I, [_VP, _LL, _I, _VP, _VP, _LL, _VP, _LL, _I, _I, _I, _VP, _F, _I, _I, _D, _VP, _VP, _VP, _I, _I, _I, _VP, _I, _I, _VP]),
+    "tlb_qk_whole_prepare": (_I, [_VP, _LL, _I, _VP, _VP, _LL, _VP, _LL, _I, _I, _I, _VP, _F, _I, _I, _D, _VP, _VP, _VP, _I, _I, _I, _VP, _VP, _VP, _I, _I, _VP]),
     "tlb_decay_scan_workspace": (ctypes.c_size_t, [_I, _I, _I, _I, _I]),
     "tlb_decay_scan": (_I, [_VP, _LL, _LL, _VP, _LL, _LL, _VP, _LL, _LL, _VP, _LL, _VP, _F, _VP, _VP, _VP, _I, _I, _F, _I, _I, _I, _VP, _I, _I, _VP, _LL, _I,
                             _VP, _VP, ctypes.c_size_t, _I, _VP, _VP, _I, _VP, _I, _VP]),
@@ -479,16 +479,22 @@ def kv_prepare(q, k, v, *, q_norm=None, k_norm=None, eps: float = 0.0, tok_pos=N
 
 
 def qk_whole_prepare(q, k, v, *, heads: int, kv_heads: int, q_norm=None, k_norm=None, eps: float = 0.0, rot_dims: int = 0, base: float = 10000.0,
-                     interleaved: bool = False, tok_pos, tok_seq=None, block_table=None, slab=None):
+                     interleaved: bool = False, tok_pos, tok_seq=None, block_table=None, slab=None, rope=None):
     """``q [T, heads * dk]`` (a view, changed in place), ``k [T, kv_heads * dk]``, ``v [T, kv_heads * dv]`` (views, or None for
     queries only): RMS norms over the WHOLE projection (weights of that size), rotation of the first ``rot_dims`` entries of
-    every head by the token's position, keys and values stored at the token's slot of ``slab [P, page, kv_heads * (dk + dv)]``."""
+    every head by the token's position, keys and values stored at the token's slot of ``slab [P, page, kv_heads * (dk + dv)]``.
+    ``rope`` = (cos, sin) of ``rope_table`` for this step's tokens: the angles are read instead of evaluated."""
     _gpu("qk_whole_prepare", q, k, v, q_norm, k_norm, tok_pos, tok_seq, block_table, slab)
     T = q.shape[0]
     dk = q.shape[1] // heads
     dv = 0
     if q.stride(1) != 1 or q.shape[1] != heads * dk or (q_norm is not None and (q_norm.shape != (heads * dk,) or q_norm.dtype != q.dtype)):
         raise RuntimeError("qk_whole_prepare: queries [T, heads * dk] with unit inner stride, a norm weight of that width")
+    cs = sn = None
+    if rope is not None and rot_dims:
+        cs, sn = rope
+        if cs.shape != (T, rot_dims // 2) or sn.shape != cs.shape or cs.dtype != torch.float32 or not cs.is_contiguous() or not sn.is_contiguous():
+            raise RuntimeError("qk_whole_prepare: rotation tables must be float32 [T, rot_dims / 2]")
     P = page_size = 0
     if k is not None:
         dv = v.shape[1] // kv_heads
@@ -500,7 +506,8 @@ def qk_whole_prepare(q, k, v, *, heads: int, kv_heads: int, q_norm=None, k_norm=
     _check(library().tlb_qk_whole_prepare(_ptr(q), q.stride(0), heads, _ptr(q_norm), _ptr(k), k.stride(0) if k is not None else 0, _ptr(v),
                                           v.stride(0) if v is not None else 0, kv_heads if k is not None else 0, dk, max(dv, 1), _ptr(k_norm), float(eps),
                                           int(rot_dims), int(bool(interleaved)), float(base), _ptr(tok_pos), _ptr(tok_seq), _ptr(block_table),
-                                          block_table.shape[1] if block_table is not None else 0, P, page_size, _ptr(slab), T, _code(q.dtype), _stream(q)))
+                                          block_table.shape[1] if block_table is not None else 0, P, page_size, _ptr(slab), _ptr(cs), _ptr(sn), T, _code(q.dtype),
+                                          _stream(q)))
 
 
 def paged_attention(q, slab, block_table, tiles, tok_pos, *, kv_heads: int, dv: int, mask: int, mask_size: int, scale: float, softcap: float = 0.0,

@@ -102,9 +102,10 @@ class PagedGroupedAttention:
         if self.whole_norm and (self.rot is None or self.rot["factor"] == 1.0):
             # each projection as ONE row: norm, rotation and the store into the cache in one launch
             r = self.rot or {"dims": 0, "base": 1.0, "interleaved": False}
+            tables = plan.rope_tables(r["dims"], r["base"]) if r["dims"] and hasattr(plan, "rope_tables") else None  # shared by the step's layers
             blocks.qk_whole_prepare(q, k if self.caches else None, v if self.caches else None, heads=H, kv_heads=G, q_norm=q_norm,
                                     k_norm=k_norm if self.caches else None, eps=self.eps, rot_dims=r["dims"], base=r["base"], interleaved=r["interleaved"],
-                                    tok_pos=plan.tok_pos, tok_seq=plan.tok_seq, block_table=plan.block_table, slab=slab if self.caches else None)
+                                    tok_pos=plan.tok_pos, tok_seq=plan.tok_seq, block_table=plan.block_table, slab=slab if self.caches else None, rope=tables)
         else:
             if self.whole_norm:  # scaled positions: the row norms alone, then the framework's rotation and store
                 blocks.kv_prepare(q.unflatten(1, (1, H * self.dim)), None, None, q_norm=q_norm, eps=self.eps)
