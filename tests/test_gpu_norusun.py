@@ -308,6 +308,31 @@ def test_norm_over_the_whole_projection_then_rotation_then_the_cache(dev, dtype,
         assert torch.equal(again, wd) and torch.equal(slab2, slab)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_whole_projection_prepare_gives_a_token_the_same_numbers_in_a_large_step_and_in_a_small_one(dev, dtype):
+    """A step of thousands of tokens takes the kernel's warp-per-token form, a small one its CTA-per-token form: bit-identical."""
+    g = torch.Generator().manual_seed(77)
+    T, heads, kv_heads, dk, dv, dims, page = 2600, 5, 1, 40, 24, 20, 64
+    q, k, v = (torch.randn(T, w, generator=g).to(dtype).to(dev) for w in (heads * dk, kv_heads * dk, kv_heads * dv))
+    wq, wk = (1 + 0.3 * torch.randn(heads * dk, generator=g)).to(dtype).to(dev), (1 + 0.3 * torch.randn(kv_heads * dk, generator=g)).to(dtype).to(dev)
+    pages = -(-T // page)
+    table = torch.arange(pages, dtype=torch.int32, device=dev).reshape(1, -1)
+    pos, seq = torch.arange(T, dtype=torch.int32, device=dev), torch.zeros(T, dtype=torch.int32, device=dev)
+
+    def run(cuts):
+        qq, slab = q.clone(), torch.zeros((pages, page, kv_heads * (dk + dv)), dtype=dtype, device=dev)
+        for lo, hi in cuts:
+            blocks.qk_whole_prepare(qq[lo:hi], k[lo:hi], v[lo:hi], heads=heads, kv_heads=kv_heads, q_norm=wq, k_norm=wk, eps=1e-6, rot_dims=dims, base=1e4,
+                                    tok_pos=pos[lo:hi], tok_seq=seq[lo:hi], block_table=table, slab=slab)
+        return qq, slab
+
+    big_q, big_slab = run([(0, T)])
+    small_q, small_slab = run([(lo, min(T, lo + 130)) for lo in range(0, T, 130)])
+    assert torch.equal(big_q, small_q) and torch.equal(big_slab, small_slab)
+    want = (O.rms_unit(q[:3].double().cpu(), 1e-6) * wq.double().cpu()).view(3, heads, dk)
+    close(big_q[:3], O.rotate(want, dims=dims, base=1e4, layout="half").reshape(3, -1), 3e-6 if dtype == torch.float32 else 1e-2)
+
+
 def fill_cache(dev, rows, page_size, dtype):
     """rows [T, width] -> (slab, block_table) with the tokens' pages in a scrambled order."""
     T, width = rows.shape

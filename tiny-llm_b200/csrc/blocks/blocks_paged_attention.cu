@@ -213,26 +213,36 @@ kv_prepare_kernel(T *q, long long q_token, long long q_head, int heads, const T 
 }
 
 // For attention whose queries and keys are RMS-normed over the WHOLE projection (all heads as one row, weights of that size)
-// and then rotated: a warp per token reads the row once into its part of shared memory as fp32, reduces the sum of squares by
-// shuffles (no CTA-wide barrier anywhere), and applies norm, weight and rotation (the first rot_dims entries of every head by
-// the token's position; pairs (2i, 2i+1) or (i, i + rot_dims/2); angles from the step's table, or evaluated in double) on the
-// way out - the queries back in place, keys and values to the token's slot of the cache.  Nothing is rounded between the norm
-// and the rotation.
-template <typename T>
+// and then rotated: W warps per token (W = 1 for launches with many tokens: no CTA-wide barrier anywhere; W = 8, a whole CTA,
+// when a step brings few tokens and a warp alone would be a long chain of loads) read the row once into shared memory as
+// fp32, reduce the sum of squares, and apply norm, weight and rotation (the first rot_dims entries of every head by the token's
+// position; pairs (2i, 2i+1) or (i, i + rot_dims/2); angles from the step's table, or evaluated in double) on the way out - the
+// queries back in place, keys and values to the token's slot of the cache.  Nothing is rounded between the norm and the
+// rotation.  The sum of squares is taken in 256 column classes (d mod 256), each class's 32-lane tree, then the eight trees in
+// order, in both forms: a token's numbers do not depend on how many tokens share its step.
+constexpr int kQkWarps = 8;
+
+template <typename T, int W>
 __global__ void __launch_bounds__(256)
 qk_whole_prepare_kernel(T *q, long long q_token, int heads, const T *__restrict__ q_norm, const T *__restrict__ k, long long k_token,
                         const T *__restrict__ v, long long v_token, int kv_heads, int dk, int dv, const T *__restrict__ k_norm, float eps, int rot_dims,
                         int interleaved, double log2_base, const int32_t *__restrict__ tok_pos, const int32_t *__restrict__ tok_seq,
                         const int32_t *__restrict__ block_table, int max_pages, int num_pages, int page_size, T *__restrict__ slab,
                         const float *__restrict__ rope_cos, const float *__restrict__ rope_sin /* [T, rot_dims / 2] tabulated, or NULL */, int tokens) {
-    extern __shared__ float smem[];  // per warp: [max(heads, kv_heads) * dk] the row, then [rot_dims] cos | sin
+    extern __shared__ float smem[];  // per token of the CTA: [max(heads, kv_heads) * dk] the row, then [rot_dims] cos | sin
+    __shared__ float partial[kQkWarps];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
-    if (t >= tokens) return;
+    const int group = W == 1 ? warp : 0, me = W == 1 ? lane : (int)threadIdx.x, step = 32 * W;  // this thread's place among its token's threads
+    const int t = W == 1 ? blockIdx.x * kQkWarps + warp : blockIdx.x;
+    if (t >= tokens) return;  // W == 8: uniform over the CTA
     const int pos = tok_pos[t], half = rot_dims / 2;
     const int longest = max(heads, kv_heads) * dk;
-    float *srow = smem + (size_t)warp * (longest + rot_dims), *cs = srow + longest, *sn = cs + half;
-    for (int i = lane; i < half; i += 32) {
+    float *srow = smem + (size_t)group * (longest + rot_dims), *cs = srow + longest, *sn = cs + half;
+    auto sync = [&]() {
+        if (W == 1) __syncwarp();
+        else __syncthreads();
+    };
+    for (int i = me; i < half; i += step) {
         if (rope_cos) cs[i] = rope_cos[(size_t)t * half + i], sn[i] = rope_sin[(size_t)t * half + i];
         else rope_angle(pos, i, rot_dims, log2_base, cs[i], sn[i]);
     }
@@ -246,19 +256,44 @@ qk_whole_prepare_kernel(T *q, long long q_token, int heads, const T *__restrict_
         const T *src = which == 0 ? q + (size_t)t * q_token : (k ? k + (size_t)t * k_token : nullptr);
         const T *w = which == 0 ? q_norm : k_norm;
         T *out = which == 0 ? q + (size_t)t * q_token : dst;
-        if (src == nullptr || out == nullptr) continue;  // uniform over the warp
+        if (src == nullptr || out == nullptr) continue;  // uniform over the token's threads
         const int width = nh * dk;
-        float ss = 0.f;
-        __syncwarp();  // the row of the pass before has been read
-        for (int d = lane; d < width; d += 32) {
-            float x = to_f(src[d]);
-            srow[d] = x;
-            ss = fmaf(x, x, ss);
+        sync();  // the row of the pass before has been read
+        float total;
+        if (W == 1) {  // a lane owns eight column classes, lane + 32 j
+            float acc[kQkWarps];
+#pragma unroll
+            for (int j = 0; j < kQkWarps; ++j) acc[j] = 0.f;
+            for (int d0 = lane; d0 < width; d0 += 32 * kQkWarps) {
+                float x[kQkWarps];
+#pragma unroll
+                for (int j = 0; j < kQkWarps; ++j) x[j] = d0 + 32 * j < width ? to_f(src[d0 + 32 * j]) : 0.f;
+#pragma unroll
+                for (int j = 0; j < kQkWarps; ++j) {
+                    if (d0 + 32 * j < width) srow[d0 + 32 * j] = x[j];
+                    acc[j] = fmaf(x[j], x[j], acc[j]);
+                }
+            }
+            total = 0.f;
+#pragma unroll
+            for (int j = 0; j < kQkWarps; ++j) total += warp_sum(acc[j]);
+        } else {       // a thread owns one column class
+            float acc = 0.f;
+            for (int d = me; d < width; d += step) {
+                float x = to_f(src[d]);
+                srow[d] = x;
+                acc = fmaf(x, x, acc);
+            }
+            acc = warp_sum(acc);
+            if (lane == 0) partial[warp] = acc;
+            __syncthreads();
+            total = 0.f;
+#pragma unroll
+            for (int j = 0; j < kQkWarps; ++j) total += partial[j];
         }
-        ss = warp_sum(ss);
-        __syncwarp();
-        const float inv = w ? 1.0f / sqrtf(ss / (float)width + eps) : 1.f;
-        for (int d = lane; d < width; d += 32) {
+        sync();
+        const float inv = w ? 1.0f / sqrtf(total / (float)width + eps) : 1.f;
+        for (int d = me; d < width; d += step) {
             const int e = d % dk;
             float x = srow[d] * inv * (w ? to_f(w[d]) : 1.f);
             if (e < rot_dims) {
@@ -273,7 +308,7 @@ qk_whole_prepare_kernel(T *q, long long q_token, int heads, const T *__restrict_
     }
     if (dst != nullptr) {
         const T *vr = v + (size_t)t * v_token;
-        for (int d = lane; d < kv_heads * dv; d += 32) dst[(size_t)kv_heads * dk + d] = vr[d];
+        for (int d = me; d < kv_heads * dv; d += step) dst[(size_t)kv_heads * dk + d] = vr[d];
     }
 }
 
@@ -363,26 +398,28 @@ int tlb_qk_whole_prepare(void *q, long long q_token, int heads, const void *q_no
     if (k && (!v || !slab || !tok_seq || !block_table || kv_heads <= 0 || dv <= 0 || page_size <= 0 || max_pages <= 0))
         return tl::fail(TL_EINVAL, "qk_whole_prepare: bad cache argument");
     if (!k) kv_heads = 0;
-    const size_t per_warp = ((size_t)(heads > kv_heads ? heads : kv_heads) * dk + rot_dims) * sizeof(float);
-    if (per_warp > 200 * 1024) return tl::fail(TL_EINVAL, "qk_whole_prepare: a projection of %d entries does not fit in shared memory", heads * dk);
-    int warps = (int)((200 * 1024) / per_warp);
-    warps = warps > 8 ? 8 : warps;
-    const size_t smem = per_warp * warps;
+    const size_t per_token = ((size_t)(heads > kv_heads ? heads : kv_heads) * dk + rot_dims) * sizeof(float);
+    if (per_token > 200 * 1024) return tl::fail(TL_EINVAL, "qk_whole_prepare: a projection of %d entries does not fit in shared memory", heads * dk);
+    // a warp per token when there are tokens enough to fill the GPU that way and eight rows fit in shared memory, else a CTA per token
+    const bool by_warp = tokens >= 148 * 8 * 2 && per_token * kQkWarps <= 200 * 1024;
+    const size_t smem = by_warp ? per_token * kQkWarps : per_token;
     double lb = rot_dims > 0 ? log2(base) : 0.0;
-#define TLB_QK                                                                                                                                      \
+#define TLB_QK_W(WV, GRID)                                                                                                                          \
     do {                                                                                                                                            \
-        auto kernel = qk_whole_prepare_kernel<T>;                                                                                                   \
+        auto kernel = qk_whole_prepare_kernel<T, WV>;                                                                                               \
         if (smem > 48 * 1024) {                                                                                                                     \
             cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                                   \
             if (e != cudaSuccess) return tl::fail(TL_ECUDA, "qk_whole_prepare: %s", cudaGetErrorString(e));                                         \
         }                                                                                                                                           \
-        kernel<<<ceil_div(tokens, warps), 32 * warps, smem, as_stream(stream)>>>((T *)q, q_token, heads, (const T *)q_norm, (const T *)k, k_token,  \
-                                                         (const T *)v, v_token, kv_heads, dk, dv, (const T *)k_norm, eps, rot_dims, interleaved, lb, \
-                                                         tok_pos, tok_seq, block_table, max_pages, num_pages, page_size, (T *)slab, rope_cos,       \
-                                                         rope_sin, tokens);                                                                         \
+        kernel<<<GRID, 32 * kQkWarps, smem, as_stream(stream)>>>((T *)q, q_token, heads, (const T *)q_norm, (const T *)k, k_token, (const T *)v,    \
+                                                         v_token, kv_heads, dk, dv, (const T *)k_norm, eps, rot_dims, interleaved, lb, tok_pos,     \
+                                                         tok_seq, block_table, max_pages, num_pages, page_size, (T *)slab, rope_cos, rope_sin,      \
+                                                         tokens);                                                                                   \
     } while (0)
+#define TLB_QK do { if (by_warp) TLB_QK_W(1, ceil_div(tokens, kQkWarps)); else TLB_QK_W(kQkWarps, tokens); } while (0)
     TLB_DISPATCH(dtype, "qk_whole_prepare", TLB_QK);
 #undef TLB_QK
+#undef TLB_QK_W
     TL_LAUNCH_CHECK("qk_whole_prepare");
     return TL_OK;
 }
