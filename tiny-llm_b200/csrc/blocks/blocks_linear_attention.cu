@@ -64,6 +64,7 @@ decay_scan_kernel(const T *__restrict__ q, long long q_token, long long q_head, 
     __shared__ float sv[kLaTokens * kLaCols];
     __shared__ float sprod[4 * KR];
     __shared__ float2 s_step[kLaTokens];  // decay_kind 3: the token's (decay, step size), worked out once per token
+    __shared__ float2 s_chan[4 * KR];     // per key channel of this head: (the decay logit's bias, the bonus), read once
     const int colblocks = (dv + kLaCols - 1) / kLaCols;
     const int s = blockIdx.x, head = blockIdx.y / colblocks, col0 = (blockIdx.y % colblocks) * kLaCols, c = blockIdx.z;
     const int seq_first = seq_info[s * 4 + 0], seq_count = seq_info[s * 4 + 1], start = seq_info[s * 4 + 2], slot = seq_info[s * 4 + 3];
@@ -90,6 +91,8 @@ decay_scan_kernel(const T *__restrict__ q, long long q_token, long long q_head, 
     }
     if (pass == 1)
         for (int d = threadIdx.x; d < dk; d += blockDim.x) sprod[d] = 1.f;
+    for (int d = threadIdx.x; d < dk; d += blockDim.x)
+        s_chan[d] = make_float2((z_bias && decay_kind != 3) ? to_f(z_bias[(size_t)head * dk + d]) : 0.f, BONUS ? to_f(bonus[(size_t)head * dk + d]) : 0.f);
     const int qk_head = head / (heads / qk_heads);
     const float rate = decay_kind == 3 ? expf(to_f(a_log[head])) : 0.f;
     const float skipv = skip ? to_f(skip[head]) : 0.f;
@@ -109,9 +112,9 @@ decay_scan_kernel(const T *__restrict__ q, long long q_token, long long q_head, 
             size_t tok = (size_t)(first + t0 + j);
             float alpha, kmul = 1.f;
             if (head_decay) alpha = head_decay[head];
-            else if (decay_kind == 2) alpha = expf(-expf(z[tok * z_token + (size_t)head * dk + d] + (z_bias ? to_f(z_bias[(size_t)head * dk + d]) : 0.f)));
+            else if (decay_kind == 2) alpha = expf(-expf(z[tok * z_token + (size_t)head * dk + d] + s_chan[d].x));
             else if (decay_kind == 3) alpha = s_step[j].x, kmul = s_step[j].y;
-            else alpha = expf(log_sigmoid(z[tok * z_token + (size_t)head * dk + d] + (z_bias ? to_f(z_bias[(size_t)head * dk + d]) : 0.f)) * inv_tau);
+            else alpha = expf(log_sigmoid(z[tok * z_token + (size_t)head * dk + d] + s_chan[d].x) * inv_tau);
             const T *kp = k + tok * k_token + (size_t)qk_head * k_head, *qp = q + tok * q_token + (size_t)qk_head * q_head;
             float kd = to_f(kp[d]), qd = to_f(qp[d]);
             if (d < rope_dims) {  // rotate the pair this entry belongs to, in fp32, by the token's tabulated angle
@@ -124,7 +127,7 @@ decay_scan_kernel(const T *__restrict__ q, long long q_token, long long q_head, 
                 qd = qd * c + to_f(qp[other]) * sn;
             }
             kd *= kmul;
-            sx[j * 4 * KR + d] = make_float4(alpha, kd, qd * q_scale, BONUS ? kd * to_f(bonus[(size_t)head * dk + d]) : 0.f);
+            sx[j * 4 * KR + d] = make_float4(alpha, kd, qd * q_scale, BONUS ? kd * s_chan[d].y : 0.f);
         }
         for (int e = threadIdx.x; e < n * kLaCols; e += blockDim.x) {
             int j = e / kLaCols, d = e - j * kLaCols;
