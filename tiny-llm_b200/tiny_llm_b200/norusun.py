@@ -134,7 +134,8 @@ class NorusunModel(RaggedDecoderModel):
                 layer.attention = PagedGroupedAttention(
                     heads=a["heads"], kv_heads=a["kv_heads"], dim=a["dim"], vdim=a["vdim"], scale=a["scale"], mask="chunk", mask_size=a["mask"]["size"],
                     w_o=take(lp + "o"), q_norm=take(lp + "q.norm"), k_norm=take(lp + "k.norm"), eps=self.eps, page_size=page_size, qk_norm="whole",
-                    rot={"dims": int(a["rot"]["dims"]), "base": float(a["rot"]["base"]), "interleaved": False}, head_bias=take(lp + "pb"), weights="sigmoid")
+                    rot=None if not (a.get("rot") or {}).get("dims") else {"dims": int(a["rot"]["dims"]), "base": float(a["rot"]["base"]), "interleaved": False},
+                    head_bias=take(lp + "pb"), weights="sigmoid")
                 layer.slab_index = len(widths)
                 widths.append(layer.attention.cache_width)
                 w_in = take(rp + "in")
